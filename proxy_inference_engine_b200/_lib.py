@@ -135,14 +135,90 @@ SIGNATURES = {
     "pie_decode_step": (_i, [_vp, _vp, _sz, _vp, _vp]),
 }
 
+
+class HybBatch(C.Structure):
+    """pieh_batch"""
+    _fields_ = [("T", C.c_int), ("n_seq", C.c_int), ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p),
+                ("seq_start", C.c_void_p), ("seq_len", C.c_void_p), ("seq_ctx", C.c_void_p), ("seq_slot", C.c_void_p),
+                ("block_table", C.c_void_p), ("bt_stride", C.c_int)]
+
+
+class HybDelta(C.Structure):
+    """pieh_delta"""
+    _fields_ = [("H", C.c_int), ("G", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("taps", C.c_int),
+                ("conv_w", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("out_norm", C.c_void_p),
+                ("eps", C.c_float), ("conv_state", C.c_void_p), ("state", C.c_void_p)]
+
+
+class HybAttn(C.Structure):
+    """pieh_attn"""
+    _fields_ = [("H", C.c_int), ("G", C.c_int), ("d", C.c_int), ("dv", C.c_int), ("rot_dims", C.c_int),
+                ("rot_freqs", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("eps", C.c_float),
+                ("scale", C.c_float), ("softcap", C.c_float), ("window", C.c_int), ("lam", C.c_float),
+                ("out_scale", C.c_float), ("k_pages", C.c_void_p), ("v_pages", C.c_void_p), ("kv_dtype", C.c_int)]
+
+
+_PB, _PD, _PA = C.POINTER(HybBatch), C.POINTER(HybDelta), C.POINTER(HybAttn)
+# libpie_b200_hybrid.so: every symbol include/pie_b200_hybrid.h declares (tests check this), + the page allocator
+HYBRID_SIGNATURES = {
+    "pieh_abi_version": (_i, []),
+    "pieh_last_cuda_error": (C.c_char_p, []),
+    "pieh_launch_count": (C.c_ulonglong, []),
+    "pieh_linear": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _i, _vp]),
+    "pieh_embed_streams": (_i, [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp]),
+    "pieh_stream_norm": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i, _vp]),
+    "pieh_stream_update": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "pieh_delta_prepare": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _ll, _PD, _PB, _vp]),
+    "pieh_delta_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _PD, _PB, _vp]),
+    "pieh_delta_gate": (_i, [_vp, _i, _vp, _vp, _ll, _ll, _PD, _i, _vp]),
+    "pieh_attn_prepare": (_i, [_vp, _vp, _ll, _PA, _PB, _vp]),
+    "pieh_attn_run": (_i, [_vp, _i, _vp, _PA, _PB, _vp]),
+}
+HYBRID_LIB_PATH = os.environ.get("PIE_HYBRID_LIB") or os.path.join(_HERE, "libpie_b200_hybrid.so")
+EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_STREAMS = 0, 1, 2, 3
+
 _lib = None
+_hyb = None
 
 
-def build(verbose: bool = False) -> str:
-    """Compile csrc/ for sm_100a into libpie_b200.so (nvcc cross-compiles without a GPU)."""
+def build(verbose: bool = False, target: str = "all") -> str:
+    """Compile csrc/ for sm_100a into libpie_b200.so and libpie_b200_hybrid.so (nvcc cross-compiles without a GPU);
+    target="hybrid" compiles the second one only.  Concurrent callers serialise on a lock file beside the sources."""
+    import fcntl
+
     out = None if verbose else subprocess.DEVNULL
-    subprocess.check_call(["make", "-s", "-j8", "-C", CSRC], stdout=out)
+    with open(os.path.join(CSRC, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        subprocess.check_call(["make", "-s", "-j8", "-C", CSRC, target], stdout=out)
     return LIB_PATH
+
+
+def load_hybrid(build_if_missing: bool = False):
+    """libpie_b200_hybrid.so.  build_if_missing: compile it on first use (the servers' and the trace runner's choice;
+    a library import stays free of side effects)."""
+    global _hyb
+    if _hyb is None:
+        if not os.path.exists(HYBRID_LIB_PATH):
+            if not build_if_missing:
+                raise RuntimeError(f"{HYBRID_LIB_PATH} is missing: build it with `make -C {CSRC} hybrid`. "
+                                   "proxy_inference_engine_b200 has no CPU fallback.")
+            build(target="hybrid")
+        L = C.CDLL(HYBRID_LIB_PATH)
+        for name, (res, args) in list(HYBRID_SIGNATURES.items()) + [(k, v) for k, v in SIGNATURES.items()
+                                                                      if k.startswith("pie_page_")]:
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _hyb = L
+    return _hyb
+
+
+def check_hybrid(status: int, what: str) -> None:
+    if status == PIE_OK:
+        return
+    msg = f"[{what}] {STATUS.get(status, status)}"
+    if status == 4:
+        raise RuntimeError(msg + ": " + load_hybrid().pieh_last_cuda_error().decode())
+    raise ValueError(msg)
 
 
 def load():

@@ -196,3 +196,64 @@ class PagedQuantizedKVCache:
         slot = (t % self.page_size)[None].expand(pages.shape[0], -1)
         pick = lambda pool: pool[pages, :, slot].permute(0, 2, 1, 3).contiguous()   # [B, T, H, .] -> [B, H, T, .]
         return tuple(map(pick, self.keys)), tuple(map(pick, self.values))
+
+
+class HybridCache:
+    """What the sequences of a recurrent / attention hybrid hold between steps, for every layer at once:
+
+    * attention layers: key / value page pools ``[pages, 64, G, 2 d]`` / ``[pages, 64, G, dv]`` in the act dtype, indexed
+      by the page ids of ONE ``paging.PageAllocator`` (a page id names the same 64 positions in every layer's pools);
+    * recurrent layers: per state slot the matrix state ``[H, dk, dv]`` and the convolution history ``[taps - 1, C]``, fp32.
+
+    ``admit`` gives a sequence a slot, ``reserve`` grows its page list to cover a length, ``release`` hands both back
+    (LIFO, so the next sequence re-uses them).  Nothing is cleared on re-use: a recurrent operator starts a sequence with
+    no context from zero whatever its slot holds, and attention never reads a position it has not written."""
+
+    page_size = 64
+
+    def __init__(self, layer_specs, max_tokens: int, max_seqs: int = 4, device="cuda", act_dtype=torch.bfloat16, lib=None):
+        from .paging import PageAllocator
+
+        self.n_pages = max(1, (int(max_tokens) + self.page_size - 1) // self.page_size)
+        self.max_seqs, self.device, self.act_dtype = int(max_seqs), device, act_dtype
+        self.allocator = PageAllocator(self.n_pages, 1, 1, lib=lib)
+        self.free_slots = list(range(self.max_seqs - 1, -1, -1))
+        self.seqs = {}     # id -> {"slot", "pages", "length"}
+        self.layers = []
+        for spec in layer_specs:
+            if spec["kind"] == "attention":
+                G, d2, dv = spec["G"], 2 * spec["d"], spec["dv"]
+                self.layers.append({"k": torch.zeros((self.n_pages, self.page_size, G, d2), dtype=act_dtype, device=device),
+                                    "v": torch.zeros((self.n_pages, self.page_size, G, dv), dtype=act_dtype, device=device)})
+            else:
+                H, dk, dv, taps, C = spec["H"], spec["dk"], spec["dv"], spec["taps"], spec["channels"]
+                self.layers.append({"state": torch.zeros((self.max_seqs, H, dk, dv), dtype=torch.float32, device=device),
+                                    "conv": torch.zeros((self.max_seqs, max(taps - 1, 1), C), dtype=torch.float32,
+                                                        device=device)})
+
+    def admit(self, seq_id):
+        if seq_id in self.seqs:
+            raise ValueError(f"sequence {seq_id} is already live")
+        if not self.free_slots:
+            raise MemoryError(f"all {self.max_seqs} state slots are in use")
+        self.seqs[seq_id] = {"slot": self.free_slots.pop(), "pages": [], "length": 0}
+        return self.seqs[seq_id]
+
+    def reserve(self, seq_id, length: int):
+        s = self.seqs[seq_id]
+        need = (length + self.page_size - 1) // self.page_size
+        if need > len(s["pages"]):
+            s["pages"] += self.allocator.allocate_pages(need - len(s["pages"]))
+        return s
+
+    def release(self, seq_id) -> None:
+        s = self.seqs.pop(seq_id)
+        if s["pages"]:
+            self.allocator.free_pages(s["pages"])
+        self.free_slots.append(s["slot"])
+
+    def can_hold(self, extra_tokens: int, length: int = 0) -> bool:
+        """Whether a sequence of ``length`` tokens can grow by ``extra_tokens`` with the pages that are free now."""
+        have = (length + self.page_size - 1) // self.page_size
+        need = (length + extra_tokens + self.page_size - 1) // self.page_size
+        return need - have <= self.allocator.get_num_free_pages()

@@ -231,12 +231,37 @@ def read_weights(path: str) -> dict:
     return weights
 
 
-def load_model(path: str, device="cuda") -> Model:
-    """PIE/models/utils.py:51-125 for the Llama family."""
+def _load_llama(config: dict, path: str, device, dtype):
+    if "quantization" not in config:
+        raise ValueError("only MLX-quantized checkpoints (config['quantization']) are on this path")
+    return build_model(ModelArgs.from_dict(config), read_weights(path), device)
+
+
+def _load_golitar(config: dict, path: str, device, dtype):
+    from .golitar import GolitarArgs, GolitarModel
+    return GolitarModel(GolitarArgs.from_dict(config), read_weights(path), device, dtype or "bfloat16")
+
+
+# model registry: config.json's "architecture" (or, for Hugging Face / MLX checkpoints, "model_type") -> loader.
+# The reference resolves model_type to a module of PIE/models/ the same way (PIE/models/utils.py:25-48).
+MODEL_REGISTRY = {"llama": _load_llama, "Golitar": _load_golitar}
+
+
+def model_kind(config: dict) -> str:
+    kind = config.get("architecture") or config.get("model_type") or "llama"
+    if kind not in MODEL_REGISTRY:
+        raise ValueError(f"Model type {kind} not supported.")
+    return kind
+
+
+def load_model(path: str, device="cuda", dtype: str | None = None):
+    """PIE/models/utils.py:51-125: read config.json, pick the model class by its type, load the safetensors.
+    dtype: "bfloat16" / "float32" for the families that run in either (None: the family's serving dtype)."""
     with open(os.path.join(path, "config.json")) as f:
         config = json.load(f)
-    if config.get("model_type", "llama") != "llama":
-        raise ValueError(f"Model type {config.get('model_type')} not supported.")
+    kind = model_kind(config)
+    if kind != "llama":
+        return MODEL_REGISTRY[kind](config, path, device, dtype)
     if "quantization" not in config:
         raise ValueError("only MLX-quantized checkpoints (config['quantization']) are on this path")
     return build_model(ModelArgs.from_dict(config), read_weights(path), device)

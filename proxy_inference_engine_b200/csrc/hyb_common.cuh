@@ -1,0 +1,62 @@
+// Shared by the hyb_*.cu operators (libpie_b200_hybrid.so): status / launch bookkeeping and typed loads.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/pie_b200_hybrid.h"
+
+namespace pieh {
+
+int status_of(cudaError_t e);   // cudaError_t -> pie_status, remembering the message
+void count_launch(int n = 1);
+int num_sms();
+
+template <typename T> struct elem;
+template <> struct elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+  static __device__ __forceinline__ float round(float v) { return v; }
+};
+template <> struct elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+  static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over the whole CTA (blockDim.x a multiple of 32, <= 1024); `red` holds 33 floats; every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float s = l < nw ? red[l] : 0.f;
+    s = warp_sum(s);
+    if (l == 0) red[32] = s;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// out dtype dispatch for host launchers
+#define PIEH_DISPATCH_DTYPE(code, T, ...)                     \
+  do {                                                        \
+    if ((code) == PIE_DTYPE_BF16) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else { using T = float; __VA_ARGS__; }                    \
+  } while (0)
+
+}  // namespace pieh

@@ -1,0 +1,230 @@
+// Gated delta rule over ragged steps: a matrix state S [dk, dv] per (sequence, head) in fp32, carried in a slot.
+//   per token:  S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+// delta_prepare_kernel  short causal convolution (history of taps - 1 inputs per sequence slot) + silu on q, k, v; q and k
+//                       to unit length (q also times dk^-1/2); beta = sigmoid(.), g = exp(-exp(A_log) softplus(. + dt_bias))
+// conv_advance_kernel   moves every sequence's convolution history past this step's rows
+// delta_scan_kernel     the recurrence: a column of S lives in the registers of R adjacent lanes (RPT rows each), so a
+//                       token costs 3 RPT multiply-adds and two log2(R)-step shuffles per thread and no barrier; the
+//                       step's q / k / v rows are staged through shared memory a chunk of tokens at a time
+// delta_gate_kernel     per-head RMS norm of o, times the norm weight, times silu(gate)
+// Everything that enters the recurrence is fp32; only delta_gate's output takes the act dtype.
+#include "hyb_common.cuh"
+
+namespace pieh {
+
+constexpr int kMaxTaps = 8;
+
+__global__ void __launch_bounds__(256) delta_prepare_kernel(float* q, float* k, float* v, float* beta, float* decay,
+                                                            const float* proj, long long ld, const pieh_delta d,
+                                                            const pieh_batch b) {
+  extern __shared__ float ch[];   // conv + silu of the q and k channels of this token
+  const int t = blockIdx.x;
+  const int i = b.tok_seq[t], start = b.seq_start[i], ctx = b.seq_ctx[i], slot = b.seq_slot[i];
+  const int j = t - start;
+  const int nq = d.G * d.dk, C = 2 * nq + d.H * d.dv, taps = d.taps;
+  const float* hist = d.conv_state + (size_t)slot * (taps - 1) * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < taps; ++r) {
+      float x;
+      if (r <= j) x = proj[(size_t)(t - r) * ld + c];
+      else {
+        const int back = r - j;   // 1 .. taps - 1 tokens before this step
+        x = ctx - back >= 0 ? hist[(size_t)(taps - 1 - back) * C + c] : 0.f;
+      }
+      acc = fmaf(d.conv_w[(size_t)c * taps + (taps - 1 - r)], x, acc);
+    }
+    const float y = silu_f(acc);
+    if (c < 2 * nq) ch[c] = y;
+    else v[(size_t)t * d.H * d.dv + (c - 2 * nq)] = y;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int hh = warp; hh < 2 * d.G; hh += nw) {   // heads of q, then heads of k
+    const float* src = ch + (size_t)hh * d.dk;
+    float ss = 0.f;
+    for (int c = lane; c < d.dk; c += 32) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    float inv = 1.f / sqrtf(ss + 1e-6f);
+    float* dst;
+    if (hh < d.G) { inv *= 1.f / sqrtf((float)d.dk); dst = q + ((size_t)t * d.G + hh) * d.dk; }
+    else dst = k + ((size_t)t * d.G + (hh - d.G)) * d.dk;
+    for (int c = lane; c < d.dk; c += 32) dst[c] = src[c] * inv;
+  }
+  if (threadIdx.x < d.H) {
+    const int h = threadIdx.x;
+    const float* row = proj + (size_t)t * ld + C + d.H * d.dv;   // behind the gate columns: b, then a
+    beta[(size_t)t * d.H + h] = 1.f / (1.f + expf(-row[h]));
+    decay[(size_t)t * d.H + h] = expf(-expf(d.A_log[h]) * softplus_f(row[d.H + h] + d.dt_bias[h]));
+  }
+}
+
+__global__ void conv_advance_kernel(const float* proj, long long ld, const pieh_delta d, const pieh_batch b) {
+  const int i = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int C = 2 * d.G * d.dk + d.H * d.dv, taps = d.taps;
+  if (c >= C) return;
+  const int start = b.seq_start[i], n = b.seq_len[i], ctx = b.seq_ctx[i];
+  float* hist = d.conv_state + (size_t)b.seq_slot[i] * (taps - 1) * C;
+  float nv[kMaxTaps];
+  for (int jj = 0; jj < taps - 1; ++jj) {
+    const int p = ctx + n - (taps - 1) + jj;   // position this entry has to hold afterwards
+    float x = 0.f;
+    if (p >= ctx) x = proj[(size_t)(start + p - ctx) * ld + c];
+    else if (p >= 0) x = hist[(size_t)(p - ctx + taps - 1) * C + c];
+    nv[jj] = x;
+  }
+  for (int jj = 0; jj < taps - 1; ++jj) hist[(size_t)jj * C + c] = nv[jj];
+}
+
+constexpr int kScanThreads = 128, kScanChunk = 16;
+
+template <int RPT>
+__global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, const float* q, const float* k, const float* v,
+                                                                  const float* beta, const float* decay,
+                                                                  const pieh_delta d, const pieh_batch b, int R) {
+  extern __shared__ float sm[];
+  const int cols = kScanThreads / R;
+  const int h = blockIdx.y, i = blockIdx.z;
+  const int hk = h / (d.H / d.G);
+  const int start = b.seq_start[i], n = b.seq_len[i], ctx = b.seq_ctx[i];
+  const int rl = threadIdx.x % R, cl = threadIdx.x / R;
+  const int j = blockIdx.x * cols + cl;           // column of S (feature of v)
+  const bool col_ok = j < d.dv;
+  const int dk = d.dk, dv = d.dv;
+  float* ks = sm;                                  // [chunk][dk]
+  float* qs = ks + kScanChunk * dk;                // [chunk][dk]
+  float* vs = qs + kScanChunk * dk;                // [chunk][cols]
+  float* gb = vs + kScanChunk * cols;              // [chunk][2]: decay, beta
+  float* S_g = d.state + (((size_t)b.seq_slot[i] * d.H + h) * dk) * dv;
+  float S[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    const int row = rl * RPT + r;
+    S[r] = (ctx > 0 && col_ok && row < dk) ? S_g[(size_t)row * dv + j] : 0.f;
+  }
+  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+    const int nc = min(kScanChunk, n - c0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < nc * dk; e += kScanThreads) {
+      const int tt = e / dk, r = e - tt * dk;
+      const size_t src = ((size_t)(start + c0 + tt) * d.G + hk) * dk + r;
+      ks[e] = k[src];
+      qs[e] = q[src];
+    }
+    for (int e = threadIdx.x; e < nc * cols; e += kScanThreads) {
+      const int tt = e / cols, c = e - tt * cols;
+      const int jj = blockIdx.x * cols + c;
+      vs[e] = jj < dv ? v[((size_t)(start + c0 + tt) * d.H + h) * dv + jj] : 0.f;
+    }
+    for (int e = threadIdx.x; e < nc; e += kScanThreads) {
+      gb[2 * e] = decay[(size_t)(start + c0 + e) * d.H + h];
+      gb[2 * e + 1] = beta[(size_t)(start + c0 + e) * d.H + h];
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nc; ++tt) {
+      const float g = gb[2 * tt], be = gb[2 * tt + 1];
+      const float* kr = ks + tt * dk + rl * RPT;
+      const float* qr = qs + tt * dk + rl * RPT;
+      float kk[RPT], pred = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        kk[r] = rl * RPT + r < dk ? kr[r] : 0.f;
+        S[r] *= g;
+        pred = fmaf(S[r], kk[r], pred);
+      }
+      for (int off = 1; off < R; off <<= 1) pred += __shfl_xor_sync(0xffffffffu, pred, off);
+      const float u = be * (vs[tt * cols + cl] - pred);
+      float out = 0.f;
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        S[r] = fmaf(kk[r], u, S[r]);
+        out = fmaf(S[r], rl * RPT + r < dk ? qr[r] : 0.f, out);
+      }
+      for (int off = 1; off < R; off <<= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
+      if (rl == 0 && col_ok) o[((size_t)(start + c0 + tt) * d.H + h) * dv + j] = out;
+    }
+  }
+  if (col_ok) {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const int row = rl * RPT + r;
+      if (row < dk) S_g[(size_t)row * dv + j] = S[r];
+    }
+  }
+}
+
+template <typename OT>
+__global__ void delta_gate_kernel(OT* out, const float* o, const float* proj, long long ld, long long gate_off,
+                                  const pieh_delta d, int T) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= T * d.H) return;
+  const int t = w / d.H, h = w - t * d.H;
+  const float* src = o + (size_t)w * d.dv;
+  float ss = 0.f;
+  for (int c = lane; c < d.dv; c += 32) ss = fmaf(src[c], src[c], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)d.dv + d.eps);
+  const float* gate = proj + (size_t)t * ld + gate_off + (size_t)h * d.dv;
+  for (int c = lane; c < d.dv; c += 32)
+    elem<OT>::store(out + (size_t)w * d.dv + c, src[c] * inv * d.out_norm[c] * silu_f(gate[c]));
+}
+
+static bool delta_ok(const pieh_delta* d) {
+  return d && d->H > 0 && d->G > 0 && d->H % d->G == 0 && d->dk > 0 && d->dv > 0 && d->taps >= 1 && d->taps <= kMaxTaps &&
+         d->dk <= 512 && d->H <= 256;
+}
+
+}  // namespace pieh
+
+using namespace pieh;
+
+extern "C" int pieh_delta_prepare(float* q, float* k, float* v, float* beta, float* decay, const float* proj, long long ld,
+                                  const pieh_delta* d, const pieh_batch* b, void* stream) {
+  if (!q || !k || !v || !beta || !decay || !proj || !d || !b) return PIE_ENULL;
+  if (!delta_ok(d)) return PIE_EINVAL_SHAPE;
+  if (b->T == 0) return PIE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)2 * d->G * d->dk * 4;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  count_launch(2);
+  delta_prepare_kernel<<<b->T, 256, smem, st>>>(q, k, v, beta, decay, proj, ld, *d, *b);
+  if (d->taps > 1) {
+    const int C = 2 * d->G * d->dk + d->H * d->dv;
+    conv_advance_kernel<<<dim3((C + 127) / 128, b->n_seq), 128, 0, st>>>(proj, ld, *d, *b);
+  }
+  return status_of(cudaGetLastError());
+}
+
+extern "C" int pieh_delta_scan(float* o, const float* q, const float* k, const float* v, const float* beta,
+                               const float* decay, const pieh_delta* d, const pieh_batch* b, void* stream) {
+  if (!o || !q || !k || !v || !beta || !decay || !d || !b) return PIE_ENULL;
+  if (!delta_ok(d)) return PIE_EINVAL_SHAPE;
+  if (b->T == 0) return PIE_OK;
+  constexpr int RPT = 16;
+  int R = 1;
+  while (R * RPT < d->dk) R <<= 1;   // lanes per column, a power of two <= 32
+  const int cols = kScanThreads / R;
+  const size_t smem = (size_t)kScanChunk * (2 * d->dk + cols + 2) * 4;
+  static bool opted = false;
+  if (smem > 48 * 1024 && !opted) {
+    cudaFuncSetAttribute(delta_scan_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    opted = true;
+  }
+  count_launch();
+  delta_scan_kernel<RPT><<<dim3((d->dv + cols - 1) / cols, d->H, b->n_seq), kScanThreads, smem, (cudaStream_t)stream>>>(
+      o, q, k, v, beta, decay, *d, *b, R);
+  return status_of(cudaGetLastError());
+}
+
+extern "C" int pieh_delta_gate(void* out, int out_dtype, const float* o, const float* proj, long long ld,
+                               long long gate_off, const pieh_delta* d, int T, void* stream) {
+  if (!out || !o || !proj || !d) return PIE_ENULL;
+  if (!delta_ok(d)) return PIE_EINVAL_SHAPE;
+  if (T == 0) return PIE_OK;
+  const long long warps = (long long)T * d->H;
+  count_launch();
+  PIEH_DISPATCH_DTYPE(out_dtype, OT, (delta_gate_kernel<OT><<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+                                          (OT*)out, o, proj, ld, gate_off, *d, T)));
+  return status_of(cudaGetLastError());
+}

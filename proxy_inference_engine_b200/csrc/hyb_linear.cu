@@ -1,0 +1,186 @@
+// Dense linear layers y = x W^T (+ bias) over unquantized weights, with the epilogues of pie_b200_hybrid.h.
+//
+// Three kernels behind pieh_linear:
+//   * linear_rows_kernel  (M <= 8: decode): a warp per output row streams the weight row once with 16-byte loads and
+//     keeps one fp32 accumulator per activation row -- bound by the weight bytes;
+//   * linear_umma_kernel  (bf16 x bf16, M >= 128, K % 64 == 0: prefill): tcgen05.mma with the fp32 accumulator in
+//     tensor memory, both operands brought into 128B-swizzled K-major shared memory by cp.async (hyb_umma.cu);
+//   * linear_tile_kernel  (everything else, and every fp32 product): 64 x 64 tiles, fp32 multiply-add on the CUDA cores.
+// With bf16 weights the activation is rounded to bf16 first, so the three agree up to the order of the fp32 sums.
+#include "hyb_common.cuh"
+
+namespace pieh {
+
+struct LinArgs {
+  void* out; long long out_ld;
+  const void* x; long long x_ld;
+  const void* w;
+  const float* bias;
+  int M, N, K, epi;
+  float epi_a;
+  const float* mix; const float* outw; int S;
+};
+
+cudaError_t launch_linear_umma(const LinArgs& a, int out_dtype, cudaStream_t st);   // hyb_umma.cu
+bool linear_umma_ok(const LinArgs& a, int x_dtype, int w_dtype);
+
+template <typename OT>
+__device__ __forceinline__ void lin_store(const LinArgs& a, int m, int n, float y) {
+  if (a.bias) y += a.bias[n];
+  if (a.epi == PIEH_EPI_RELU2) { y = fmaxf(y, 0.f); y = y * y; }
+  else if (a.epi == PIEH_EPI_SOFTCAP) y = a.epi_a * tanhf(y / a.epi_a);
+  if (a.epi == PIEH_EPI_STREAMS) {
+    float* xs = reinterpret_cast<float*>(a.out) + (size_t)m * a.S * a.N + n;
+    float old[8];
+    for (int s = 0; s < a.S; ++s) old[s] = xs[(size_t)s * a.N];
+    for (int u = 0; u < a.S; ++u) {
+      float acc = a.outw[u] * y;
+      for (int s = 0; s < a.S; ++s) acc = fmaf(a.mix[s * a.S + u], old[s], acc);
+      xs[(size_t)u * a.N] = acc;
+    }
+    return;
+  }
+  elem<OT>::store(reinterpret_cast<OT*>(a.out) + (size_t)m * a.out_ld + n, y);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+template <typename XT, typename WT, typename OT>
+__global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4], Ws[BK][BN + 4];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const XT* x = reinterpret_cast<const XT*>(a.x);
+  const WT* w = reinterpret_cast<const WT*>(a.w);
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < a.K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = tid + i * 256, r = e >> 4, c = e & 15;   // r: tile row, c: k within the step
+      const int k = k0 + c;
+      float xv = 0.f, wv = 0.f;
+      if (k < a.K) {
+        if (m0 + r < a.M) {
+          xv = elem<XT>::load(x + (size_t)(m0 + r) * a.x_ld + k);
+          xv = elem<WT>::round(xv);   // bf16 weights: bf16 x bf16 products, exact in fp32
+        }
+        if (n0 + r < a.N) wv = elem<WT>::load(w + (size_t)(n0 + r) * a.K + k);
+      }
+      As[c][r] = xv;
+      Ws[c][r] = wv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < BK; ++c) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { av[i] = As[c][ty * 4 + i]; wv[i] = Ws[c][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+      if (m < a.M && n < a.N) lin_store<OT>(a, m, n, acc[i][j]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// M <= 8.  A warp per output row; a lane takes 8 consecutive k per round (16 bytes of bf16, 32 of fp32).
+template <typename T> struct vec8;
+template <> struct vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+template <> struct vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+};
+
+template <typename XT, typename WT, typename OT, int MR>
+__global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp;
+  if (n >= a.N) return;
+  const XT* x = reinterpret_cast<const XT*>(a.x);
+  const WT* w = reinterpret_cast<const WT*>(a.w) + (size_t)n * a.K;
+  float acc[MR];
+#pragma unroll
+  for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+  for (int k = lane * 8; k < a.K; k += 256) {
+    float wv[8];
+    vec8<WT>::load(w + k, wv);
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+      if (m < a.M) {
+        float xv[8];
+        vec8<XT>::load(x + (size_t)m * a.x_ld + k, xv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[m] = fmaf(elem<WT>::round(xv[i]), wv[i], acc[m]);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MR; ++m) {
+    const float y = warp_sum(acc[m]);
+    if (lane == 0 && m < a.M) lin_store<OT>(a, m, n, y);
+  }
+}
+
+template <typename XT, typename WT, typename OT>
+static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
+  const bool vec_ok = a.K % 8 == 0 && a.x_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 31) == 0 &&
+                      (reinterpret_cast<uintptr_t>(a.w) & 31) == 0;
+  count_launch();
+  if (a.M <= 8 && vec_ok) {
+    const int grid = (a.N + 7) / 8;
+    if (a.M <= 1) linear_rows_kernel<XT, WT, OT, 1><<<grid, 256, 0, st>>>(a);
+    else if (a.M <= 4) linear_rows_kernel<XT, WT, OT, 4><<<grid, 256, 0, st>>>(a);
+    else linear_rows_kernel<XT, WT, OT, 8><<<grid, 256, 0, st>>>(a);
+  } else {
+    const dim3 grid((a.N + 63) / 64, (a.M + 63) / 64);
+    linear_tile_kernel<XT, WT, OT><<<grid, 256, 0, st>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace pieh
+
+using namespace pieh;
+
+extern "C" int pieh_linear(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld,
+                           const void* w, int w_dtype, const float* bias, int M, int N, int K, int epilogue, float epi_a,
+                           const float* mix, const float* outw, int S, void* stream) {
+  if (!out || !x || !w) return PIE_ENULL;
+  if (M < 0 || N <= 0 || K <= 0) return PIE_EINVAL_SHAPE;
+  if (M == 0) return PIE_OK;
+  if (epilogue < 0 || epilogue > PIEH_EPI_STREAMS) return PIE_EUNSUPPORTED;
+  if (epilogue == PIEH_EPI_STREAMS && (!mix || !outw || S < 1 || S > 8 || out_dtype != PIE_DTYPE_F32)) return PIE_EINVAL_SHAPE;
+  if (epilogue == PIEH_EPI_SOFTCAP && !(epi_a > 0.f)) return PIE_EINVAL_SHAPE;
+  if (w_dtype == PIE_DTYPE_F32 && x_dtype != PIE_DTYPE_F32) return PIE_EINVAL_DTYPE;   // exact mode is fp32 end to end
+  LinArgs a{out, out_ld, x, x_ld, w, bias, M, N, K, epilogue, epi_a, mix, outw, S};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (linear_umma_ok(a, x_dtype, w_dtype)) return status_of(launch_linear_umma(a, out_dtype, st));
+  typedef __nv_bfloat16 bf;
+  cudaError_t e;
+  if (w_dtype == PIE_DTYPE_F32) {
+    e = out_dtype == PIE_DTYPE_F32 ? launch_typed<float, float, float>(a, st) : launch_typed<float, float, bf>(a, st);
+  } else if (x_dtype == PIE_DTYPE_F32) {
+    e = out_dtype == PIE_DTYPE_F32 ? launch_typed<float, bf, float>(a, st) : launch_typed<float, bf, bf>(a, st);
+  } else {
+    e = out_dtype == PIE_DTYPE_F32 ? launch_typed<bf, bf, float>(a, st) : launch_typed<bf, bf, bf>(a, st);
+  }
+  return status_of(e);
+}

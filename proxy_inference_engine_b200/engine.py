@@ -1,0 +1,109 @@
+"""Continuous-batching engine for models that step over ``ragged.BatchDetails`` with a ``cache.HybridCache``
+(``golitar.GolitarModel``): the generate loop of PIE (PIE/engine/inference_engine.py:228-297) lifted from one sequence to
+a changing set of them.
+
+    eng = HybridEngine(model, max_tokens=4096, max_seqs=4)
+    outs = eng.generate([prompt_a, prompt_b, ...], max_new_tokens=32)           # greedy; sampler=make_sampler(...)
+
+Scheduling policy of ``generate``: every step carries one token of each sequence that is decoding plus portions of
+waiting prompts up to ``step_tokens`` rows; a prompt is admitted when a state slot and the pages of its whole length
+(prompt + new tokens) are free, and hands both back when it ends, so later prompts re-use them.  ``forward`` is the
+step underneath, also usable on its own: the caller names which sequences advance by which tokens (replay of a recorded
+schedule, speculative verification, scoring)."""
+from __future__ import annotations
+
+import torch
+
+from .ragged import BatchDetails
+
+
+class HybridEngine:
+    def __init__(self, model, max_tokens: int, max_seqs: int = 4):
+        self.model = model
+        self.cache = model.make_cache(max_tokens, max_seqs)
+        self.device = model.device
+
+    # ---- one step ----------------------------------------------------------------------------------
+    def forward(self, entries, trace=None) -> torch.Tensor:
+        """entries: [(seq_id, new_token_ids, wanted)] with ``wanted`` the indices into new_token_ids whose logits are
+        asked for (None: the last one).  Unknown ids are admitted.  Returns fp32 logits [total wanted, vocab] in entry
+        order (an empty tensor if nothing is wanted; the step still runs and advances every sequence)."""
+        seqs, rows, row0 = [], [], 0
+        for sid, toks, want in entries:
+            toks = [int(t) for t in toks]
+            if not toks:
+                raise ValueError(f"sequence {sid}: no tokens in this step")
+            if sid not in self.cache.seqs:
+                self.cache.admit(sid)
+            s = self.cache.reserve(sid, self.cache.seqs[sid]["length"] + len(toks))
+            seqs.append((sid, toks, s["length"], list(s["pages"]), s["slot"]))
+            want = [len(toks) - 1] if want is None else [int(w) for w in want]
+            for w in want:
+                if not 0 <= w < len(toks):
+                    raise ValueError(f"sequence {sid}: wanted row {w} outside its {len(toks)} tokens")
+            rows += [row0 + w for w in want]
+            row0 += len(toks)
+        batch = BatchDetails.build(seqs, device=self.device)
+        # with nothing wanted the head still needs a row: take the last and drop the result
+        idx = torch.tensor(rows if rows else [row0 - 1], dtype=torch.int32).to(self.device)
+        logits = self.model.step(batch, self.cache, rows=idx, trace=trace)
+        for sid, toks, *_ in seqs:
+            self.cache.seqs[sid]["length"] += len(toks)
+        return logits if rows else logits[:0]
+
+    def finish(self, seq_id) -> None:
+        self.cache.release(seq_id)
+
+    # ---- scheduler ---------------------------------------------------------------------------------
+    def generate(self, prompts, max_new_tokens: int, sampler=None, step_tokens: int = 512, eos: int | None = None):
+        """Greedy (sampler None) or sampled continuation of every prompt; returns the new tokens per prompt.
+        sampler: ``samplers.make_sampler(...)`` -- bf16 logits [rows, vocab] -> int32 [rows] on the device."""
+        if sampler is None:
+            from .samplers import make_sampler
+            sampler = make_sampler(0.0)
+        waiting = list(range(len(prompts)))          # prompt indices not admitted yet, in order
+        live = {}                                    # index -> {"fed": prompt tokens already in the cache, "next": token}
+        out = [[] for _ in prompts]
+        while waiting or live:
+            while waiting and self.cache.free_slots:
+                i = waiting[0]
+                if not self._room_for(live, prompts, max_new_tokens, i):
+                    break
+                waiting.pop(0)
+                self.cache.admit(("gen", i))
+                live[i] = {"fed": 0, "next": None}
+            if not live:
+                raise MemoryError("a prompt does not fit the engine's page pool")
+            entries, takers, budget = [], [], step_tokens
+            for i, s in live.items():                # decoding sequences first: one row each
+                if s["next"] is not None:
+                    entries.append((("gen", i), [s["next"]], None))
+                    takers.append(i)
+                    budget -= 1
+            for i, s in live.items():                # then prompt portions while rows are left
+                if s["next"] is None and budget > 0:
+                    n = min(budget, len(prompts[i]) - s["fed"])
+                    part = prompts[i][s["fed"]: s["fed"] + n]
+                    s["fed"] += n
+                    budget -= n
+                    done = s["fed"] == len(prompts[i])
+                    entries.append((("gen", i), part, None if done else []))
+                    if done:
+                        takers.append(i)
+            logits = self.forward(entries)
+            if takers:
+                toks = sampler(logits.to(torch.bfloat16)).tolist()
+                for i, tok in zip(takers, toks):
+                    out[i].append(int(tok))
+                    live[i]["next"] = int(tok)
+                    if len(out[i]) >= max_new_tokens or (eos is not None and tok == eos):
+                        self.finish(("gen", i))
+                        del live[i]
+        return out
+
+    def _room_for(self, live, prompts, max_new_tokens, i) -> bool:
+        """Pages for the whole life of prompt i beside what the live sequences may still claim."""
+        ps = self.cache.page_size
+        pages = lambda n: (n + ps - 1) // ps
+        claimed = sum(pages(len(prompts[j]) + max_new_tokens) - len(self.cache.seqs[("gen", j)]["pages"]) for j in live)
+        return pages(len(prompts[i]) + max_new_tokens) + claimed <= self.cache.allocator.get_num_free_pages()

@@ -23,14 +23,16 @@ PAGE_TOKENS = 64   # TOKEN_CAPACITY_PER_PAGE (page.hpp:14)
 
 
 class PageAllocator:
-    def __init__(self, num_pages: int, num_heads: int, head_dim: int):
+    def __init__(self, num_pages: int, num_heads: int, head_dim: int, lib=None):
+        """lib: the loaded library that carries the allocator (libpie_b200.so by default; libpie_b200_hybrid.so links
+        the same code, so a hybrid model's server needs only that one)."""
         if num_pages <= 0:
             raise ValueError("PageAllocator must be initialized with num_pages > 0.")     # page_allocator.cpp:21-23
         if num_heads <= 0:
             raise ValueError("num_heads must be positive.")
         if head_dim <= 0:
             raise ValueError("head_dim must be positive.")
-        self._L = _lib.load()
+        self._L = lib if lib is not None else _lib.load()
         self._h = self._L.pie_page_allocator_create(num_pages, num_heads, head_dim)
         if not self._h:
             raise MemoryError("pie_page_allocator_create failed")

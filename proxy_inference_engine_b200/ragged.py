@@ -40,6 +40,7 @@ class BatchDetails:
     num_prefill_sequences: int = 0
     num_decode_sequences: int = 0
     total_tokens_in_step: int = 0
+    state_slots: list = field(default_factory=list)        # per sequence: slot of its recurrent state (hybrid models)
 
     @classmethod
     def build(cls, sequences, device="cuda") -> "BatchDetails":
@@ -47,7 +48,9 @@ class BatchDetails:
         the sequence already in the cache; ``page_ids`` must cover context_length + len(new_token_ids) tokens."""
         ids, pos, sids, ins, ctxs, rows = [], [], [], [], [], []
         n_pre = n_dec = 0
-        for sid, toks, ctx, pages in sequences:
+        slots = []
+        for sid, toks, ctx, pages, *rest in sequences:
+            slots.append(int(rest[0]) if rest else 0)
             toks = [int(t) for t in toks]
             if not toks:
                 raise ValueError(f"sequence {sid}: no tokens in this step")
@@ -67,10 +70,10 @@ class BatchDetails:
                 n_dec += 1
         if not sids:
             raise ValueError("empty batch")
-        width = max(len(r) for r in rows)
+        width = max(1, max(len(r) for r in rows))
         table = torch.tensor([r + [0] * (width - len(r)) for r in rows], dtype=torch.int32)
         return cls(torch.tensor(ids, dtype=torch.int32).to(device), torch.tensor(pos, dtype=torch.int32).to(device), sids,
-                   ins, ctxs, table.to(device), n_pre, n_dec, len(ids))
+                   ins, ctxs, table.to(device), n_pre, n_dec, len(ids), slots)
 
     def validate(self) -> None:
         n = len(self.sequence_ids)
@@ -95,6 +98,25 @@ class BatchDetails:
             acc += n
             ends.append(acc - 1)
         return torch.tensor(ends, dtype=torch.long, device=self.token_ids.device)
+
+    def hybrid_descriptor(self):
+        """The step as libpie_b200_hybrid.so reads it (pieh_batch): per-row sequence index and position, per-sequence
+        first row / rows / context / state slot, and the block table.  One host-to-device copy; returns (struct, keepalive)."""
+        from ._lib import HybBatch
+        n, T = len(self.sequence_ids), self.total_tokens_in_step
+        starts, acc = [], 0
+        for m in self.input_lengths:
+            starts.append(acc)
+            acc += m
+        tok_seq = [i for i, m in enumerate(self.input_lengths) for _ in range(m)]
+        slots = list(self.state_slots) if self.state_slots else [0] * n
+        host = torch.tensor(tok_seq + starts + list(self.input_lengths) + list(self.context_lengths) + slots,
+                            dtype=torch.int32)
+        dev = host.to(self.token_ids.device)
+        ptr = lambda off: dev.data_ptr() + 4 * off
+        d = HybBatch(T, n, ptr(0), self.positions.data_ptr(), ptr(T), ptr(T + n), ptr(T + 2 * n), ptr(T + 3 * n),
+                     self.consolidated_block_table.data_ptr(), self.consolidated_block_table.stride(0))
+        return d, (dev, self.positions, self.consolidated_block_table)
 
     def token_block_table(self) -> torch.Tensor:
         """[total_tokens, max_blocks]: the block-table row of each token's sequence (what the kernels index by row)."""
