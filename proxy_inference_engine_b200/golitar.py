@@ -134,10 +134,11 @@ class GolitarModel:
                 H, G, dk, dv, taps = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"]), int(m.get("conv") or 1)
                 ly["proj"] = _Linear(torch.cat([mw("q"), mw("k"), mw("v"), mw("g"), mw("b"), mw("a")], 0), None,
                                      self.exact, device)
-                if taps > 1:
+                if opt("q.conv") is not None:
                     conv = torch.cat([mw("q.conv"), mw("k.conv"), mw("v.conv")], 0)
+                    taps = int(conv.shape[1])
                 else:
-                    conv = torch.ones((2 * G * dk + H * dv, 1))
+                    taps, conv = 1, torch.ones((2 * G * dk + H * dv, 1))
                 ly["conv_w"] = f32(conv)
                 ly["A_log"], ly["dt_bias"], ly["out_norm"] = f32(mw("A_log")), f32(mw("dt_bias")), f32(mw("norm"))
                 ly["out"] = _Linear(mw("o"), None, self.exact, device)
@@ -287,7 +288,7 @@ def random_weights(args: GolitarArgs, seed: int = 0) -> dict:
             H, G, dk, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m.get("conv") or 1
             for n, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
                 w[p + "mix." + n] = lin(rows, W)
-                if taps > 1:
+                if m.get("conv"):
                     w[p + f"mix.{n}.conv"] = (rnd(rows, taps) / math.sqrt(taps) + torch.eye(taps)[-1]).to(bf)
             w[p + "mix.g"], w[p + "mix.b"], w[p + "mix.a"] = lin(H * dv, W), lin(H, W), lin(H, W)
             w[p + "mix.A_log"] = torch.log(0.5 + 4 * torch.rand(H, generator=g)).to(bf)

@@ -25,10 +25,6 @@ def norm_centered(x, w, eps):
     return unit_rms(x, eps) * (1.0 + w)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def silu(z):
     return z * torch.sigmoid(z)
 
@@ -66,7 +62,7 @@ def delta_mixer(h, weights, p, m, eps):
     proj = {}
     for n in ("q", "k", "v"):
         z = h @ _w(weights, p + n).T
-        proj[n] = silu(causal_conv(z, _w(weights, p + n + ".conv")))
+        proj[n] = silu(causal_conv(z, _w(weights, p + n + ".conv")) if (p + n + ".conv") in weights else z)
     q = proj["q"].view(T, G, dk)
     k = proj["k"].view(T, G, dk)
     v = proj["v"].view(T, H, dv)

@@ -1,0 +1,324 @@
+"""Golitar on the GPU against the plain float64 restatement of tests/golitar_oracle.py: every mechanism in a model of
+its own, prompts against token-by-token decoding, portions, mixed batches, re-used pages and slots, the edges of
+windows and pages, long-range memory of the recurrence, odd sizes, and greedy generation through the engine."""
+import copy
+
+import pytest
+import torch
+
+import golitar_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DELTA = {"type": "delta", "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 40, "conv": 3}, "mlp": None}
+ATTN = {"type": "attention", "mlp": None,
+        "mixer": {"heads": 6, "kv_heads": 2, "dim": 24, "vdim": 40, "diff": 0.2, "scale": 0.3, "softcap": 30.0,
+                  "mask": {"size": 9},
+                  "rot": {"base": 10000.0, "dims": 12,
+                          "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}}}}
+FF = {"kind": "dense", "ff": 136}
+
+
+def make(layers, width=72, vocab=203, streams=3, seed=0, dtype="float32", cap=12.0, **kw):
+    from proxy_inference_engine_b200.golitar import GolitarArgs, GolitarModel, random_weights
+    cfg = {"architecture": "Golitar", "vocab": vocab, "width": width, "streams": streams, "norm": {"eps": 1e-5},
+           "layers": copy.deepcopy(layers)}
+    if cap:
+        cfg["logit_softcap"] = cap
+    args = GolitarArgs.from_dict(cfg)
+    w = random_weights(args, seed=seed)
+    for name, fn in (kw.get("edit") or {}).items():
+        w[name] = fn(w[name]).to(torch.bfloat16)
+    return cfg, w, GolitarModel(args, w, "cuda", dtype)
+
+
+def engine(model, max_tokens=1024, max_seqs=4):
+    from proxy_inference_engine_b200.engine import HybridEngine
+    return HybridEngine(model, max_tokens, max_seqs)
+
+
+def toks(n, vocab=203, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def err(got, want):
+    """rms of the difference over rms of the reference, per row, worst row."""
+    got, want = got.double().cpu(), want.double()
+    return float(((got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-9)).max())
+
+
+def whole(eng, ids, sid="w"):
+    out = eng.forward([(sid, ids, list(range(len(ids))))])
+    eng.finish(sid)
+    return out
+
+
+TOL32, TOL16 = 2e-4, 4e-2
+
+
+# ---- each mechanism in a model of its own ---------------------------------------------------------------------------
+@pytest.mark.parametrize("layers", [[DELTA], [ATTN], [dict(DELTA, mlp=FF)], [dict(ATTN, mlp=FF)], [DELTA, ATTN, DELTA]],
+                         ids=["delta", "attention", "delta+ff", "attention+ff", "stack"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_match_the_oracle(layers, dtype):
+    cfg, w, model = make(layers, dtype=dtype)
+    ids = toks(37)
+    trace = []
+    eng = engine(model)
+    got = eng.forward([("a", ids, list(range(len(ids))))], trace=trace)
+    want, want_layers = O.forward(cfg, w, ids, return_layers=True)
+    tol = TOL32 if dtype == "float32" else TOL16
+    for i, t in enumerate(trace):
+        assert err(t, want_layers[i]) < tol, f"residual after layer {i}"
+    assert err(got, want) < tol
+
+
+@pytest.mark.parametrize("streams", [1, 2, 5])
+def test_residual_streams(streams):
+    cfg, w, model = make([dict(DELTA, mlp=FF), dict(ATTN, mlp=FF)], streams=streams)
+    ids = toks(20)
+    assert err(whole(engine(model), ids), O.forward(cfg, w, ids)) < TOL32
+
+
+def test_plain_residual_without_stream_weights():
+    from proxy_inference_engine_b200.golitar import GolitarArgs, GolitarModel, random_weights
+    cfg = {"architecture": "Golitar", "vocab": 120, "width": 64, "norm": {"eps": 1e-6}, "layers": [dict(DELTA, mlp=FF), ATTN]}
+    w = {k: v for k, v in random_weights(GolitarArgs.from_dict(cfg), seed=3).items() if ".hc" not in k}
+    model = GolitarModel(GolitarArgs.from_dict(cfg), w, "cuda", "float32")
+    ids = toks(19, 120)
+    assert err(whole(engine(model), ids), O.forward(cfg, w, ids)) < TOL32
+
+
+def test_linear_kernels_agree_with_a_plain_product():
+    """The three shapes of pieh_linear (few rows, tiles, ragged edges) in both precisions, with bias and epilogues."""
+    import ctypes as C
+    from proxy_inference_engine_b200 import _lib
+    L = _lib.load_hybrid(build_if_missing=True)
+    g = torch.Generator().manual_seed(0)
+    for M, N, K in [(1, 96, 64), (3, 50, 200), (8, 130, 72), (9, 64, 64), (70, 100, 99), (200, 300, 256)]:
+        for exact in (True, False):
+            x = torch.randn((M, K), generator=g).cuda()
+            wt = (torch.randn((N, K), generator=g) / K ** 0.5).to(torch.bfloat16)
+            bias = torch.randn((N,), generator=g).cuda()
+            wd = wt.float().cuda() if exact else wt.cuda()
+            for epi in (0, 1, 2):
+                out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+                st = L.pieh_linear(C.c_void_p(out.data_ptr()), 1, N, C.c_void_p(x.data_ptr()), 1, K, C.c_void_p(wd.data_ptr()),
+                                   1 if exact else 0, C.c_void_p(bias.data_ptr()), M, N, K, epi, 5.0, None, None, 0, None)
+                assert st == 0
+                xr = x.double().cpu() if exact else x.to(torch.bfloat16).double().cpu()
+                y = xr @ wt.double().T + bias.double().cpu()
+                y = torch.relu(y) ** 2 if epi == 1 else (5.0 * torch.tanh(y / 5.0) if epi == 2 else y)
+                assert err(out, y) < 1e-5, (M, N, K, exact, epi)
+
+
+# ---- schedules ------------------------------------------------------------------------------------------------------
+HYBRID = [dict(DELTA, mlp=None), dict(ATTN, mlp=FF), DELTA]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompt_then_token_by_token(dtype):
+    cfg, w, model = make(HYBRID, dtype=dtype)
+    ids = toks(90)
+    want = O.forward(cfg, w, ids)
+    eng = engine(model)
+    rows = [eng.forward([("a", ids[:50], None)])]
+    for t in range(50, 90):
+        rows.append(eng.forward([("a", [ids[t]], [0])]))
+    tol = TOL32 if dtype == "float32" else TOL16
+    assert err(torch.cat(rows), want[49:]) < tol
+
+
+@pytest.mark.parametrize("sizes", [[2] * 20, [1, 2, 3, 5, 7, 11, 2, 9], [63, 2, 64, 1], [64, 64], [5, 70, 2]])
+def test_portions_of_any_size(sizes):
+    cfg, w, model = make(HYBRID)
+    ids = toks(sum(sizes))
+    want = O.forward(cfg, w, ids)
+    eng = engine(model)
+    at, got = 0, []
+    for n in sizes:
+        got.append(eng.forward([("a", ids[at:at + n], list(range(n)))]))
+        at += n
+    assert err(torch.cat(got), want) < TOL32
+
+
+def test_unequal_requests_in_one_batch_equal_each_alone():
+    cfg, w, model = make(HYBRID)
+    seqs = {"a": toks(130, seed=2), "b": toks(7, seed=3), "c": toks(66, seed=4), "d": toks(1, seed=5)}
+    want = {k: O.forward(cfg, w, v) for k, v in seqs.items()}
+    eng = engine(model, max_tokens=64 * 7)
+    # step 1: portions of a, b (whole), c; step 2: the rest of a and c beside d's only token; step 3: single tokens
+    s1 = eng.forward([("a", seqs["a"][:100], [99]), ("b", seqs["b"], [0, 6]), ("c", seqs["c"][:3], [2])])
+    s2 = eng.forward([("a", seqs["a"][100:129], [0, 28]), ("d", seqs["d"], [0]), ("c", seqs["c"][3:65], [61])])
+    s3 = eng.forward([("c", seqs["c"][65:], [0]), ("a", seqs["a"][129:], [0])])
+    got = torch.cat([s1, s2, s3])
+    ref = torch.stack([want["a"][99], want["b"][0], want["b"][6], want["c"][2], want["a"][100], want["a"][128],
+                       want["d"][0], want["c"][64], want["c"][65], want["a"][129]])
+    assert err(got, ref) < TOL32
+
+
+def test_pages_and_slots_are_used_again():
+    """Two slots and four pages for six requests in turn: every later request lands on a slot and pages that still hold
+    an earlier one's state, and must not see it."""
+    cfg, w, model = make(HYBRID)
+    eng = engine(model, max_tokens=64 * 4, max_seqs=2)
+    used_slots, used_pages = set(), set()
+    for r in range(6):
+        ids = toks(70 + 9 * r, seed=10 + r)
+        want = O.forward(cfg, w, ids)
+        a = eng.forward([(r, ids[:33], [32])])
+        used_slots.add(eng.cache.seqs[r]["slot"]); used_pages.update(eng.cache.seqs[r]["pages"])
+        b = eng.forward([(r, ids[33:], None)])
+        assert err(torch.cat([a, b]), torch.stack([want[32], want[-1]])) < TOL32, r
+        if r % 2:                      # keep one alive over the next admission so slots alternate
+            eng.finish(r)
+            eng.finish(r - 1)
+    assert len(used_slots) == 2 and len(used_pages) <= 4
+
+
+def test_a_freed_slot_does_not_leak_its_state():
+    cfg, w, model = make([DELTA])
+    eng = engine(model, max_seqs=1)
+    eng.forward([("x", toks(40, seed=7), None)])
+    eng.finish("x")
+    ids = toks(5, seed=8)
+    assert err(whole(eng, ids), O.forward(cfg, w, ids)) < TOL32
+
+
+# ---- edges ----------------------------------------------------------------------------------------------------------
+def _peaky(window):
+    """One attention layer whose scores are large, so that a single key inside or outside the window shows."""
+    a = copy.deepcopy(ATTN)
+    a["mixer"]["mask"] = {"size": window}
+    a["mixer"]["scale"] = 1.0
+    a["mixer"]["softcap"] = 40.0
+    big = lambda t: t.float() * 4.0
+    return [a], {"l0.mix.q.norm": big, "l0.mix.k.norm": big}
+
+
+@pytest.mark.parametrize("window,n", [(9, 30), (64, 140), (65, 140), (1, 12), (100, 260)])
+def test_window_edge_in_prompt_and_in_decoding(window, n):
+    layers, edit = _peaky(window)
+    cfg, w, model = make(layers, edit=edit)
+    base = toks(n, seed=20)
+    last = n - 1
+    for back, seen in ((window - 1, True), (window, False)):
+        if last - back < 0:
+            continue
+        alt = list(base)
+        alt[last - back] = (alt[last - back] + 17) % 203
+        ref_a, ref_b = O.forward(cfg, w, base)[last], O.forward(cfg, w, alt)[last]
+        moved = float((ref_a - ref_b).abs().max())
+        if seen and window > 1:
+            assert moved > 1e-3, "the planted key must matter for this test to mean anything"
+        if not seen:
+            assert moved < 1e-12
+        for ids, ref in ((base, ref_a), (alt, ref_b)):
+            eng = engine(model)
+            p = eng.forward([("p", ids, [last])])                          # as a prompt
+            eng.forward([("d", ids[:last - 3], [])])                          # decoded: last 4 tokens one by one
+            for t in range(last - 3, last + 1):
+                d = eng.forward([("d", [ids[t]], [0])])
+            assert err(p, ref[None]) < TOL32 and err(d, ref[None]) < TOL32, (back, seen)
+
+
+def test_no_window_no_rotation_no_caps():
+    a = copy.deepcopy(ATTN)
+    for k in ("mask", "rot", "softcap"):
+        a["mixer"].pop(k)
+    cfg, w, model = make([a], cap=None)
+    ids = toks(150)
+    assert err(whole(engine(model), ids), O.forward(cfg, w, ids)) < TOL32
+
+
+def test_recurrence_remembers_the_first_token_over_hundreds():
+    """Decay close to one: the first token's write is still read 400 tokens later, through prompt portions and decoding."""
+    slow = {"l0.mix.A_log": lambda t: torch.full_like(t.float(), -9.0)}
+    wide = {"type": "delta", "mixer": {"heads": 2, "kv_heads": 1, "dim": 128, "vdim": 16, "conv": 3}, "mlp": None}
+    cfg, w, model = make([wide], edit=slow)   # wide keys: later writes overlap the first one little
+    base = toks(400, seed=30)
+    alt = [(base[0] + 5) % 203] + base[1:]
+    ref_a, ref_b = O.forward(cfg, w, base)[-1], O.forward(cfg, w, alt)[-1]
+    assert float((ref_a - ref_b).abs().max()) > 1e-2
+    for ids, ref in ((base, ref_a), (alt, ref_b)):
+        eng = engine(model)
+        eng.forward([("s", ids[:3], []), ])
+        eng.forward([("s", ids[3:350], [])])
+        for t in range(350, 400):
+            out = eng.forward([("s", [ids[t]], [0])])
+        assert err(out, ref[None]) < TOL32
+
+
+def test_first_tokens_and_single_token_sequences():
+    cfg, w, model = make(HYBRID)
+    for n in (1, 2, 3):
+        ids = toks(n, seed=40 + n)
+        assert err(whole(engine(model), ids), O.forward(cfg, w, ids)) < TOL32
+    ids = toks(6, seed=44)
+    eng = engine(model)
+    got = torch.cat([eng.forward([("a", [t], [0])]) for t in ids])       # decoding from the very first token
+    assert err(got, O.forward(cfg, w, ids)) < TOL32
+
+
+def test_long_decoding():
+    cfg, w, model = make(HYBRID, dtype="bfloat16")
+    ids = toks(300, seed=50)
+    eng = engine(model)
+    eng.forward([("a", ids[:20], [])])
+    got = torch.cat([eng.forward([("a", [t], [0])]) for t in ids[20:]])
+    assert err(got, O.forward(cfg, w, ids)[20:]) < TOL16
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_other_sizes(case):
+    d = {"type": "delta", "mlp": None}
+    a = {"type": "attention", "mlp": None}
+    cases = [
+        dict(layers=[dict(d, mixer={"heads": 1, "kv_heads": 1, "dim": 8, "vdim": 8, "conv": 2}),
+                     dict(a, mixer=dict(ATTN["mixer"], heads=1, kv_heads=1, dim=8, vdim=16, rot={"base": 100.0, "dims": 8}))],
+             width=64, vocab=64, streams=1),
+        dict(layers=[dict(d, mixer={"heads": 6, "kv_heads": 3, "dim": 80, "vdim": 48, "conv": 5}, mlp={"kind": "dense", "ff": 50})],
+             width=100, vocab=77, streams=2),
+        dict(layers=[dict(a, mixer=dict(ATTN["mixer"], heads=8, kv_heads=8, dim=16, vdim=128, mask={"size": 33}), mlp=FF),
+                     dict(d, mixer={"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 130})],
+             width=128, vocab=300, streams=4),
+        dict(layers=[dict(a, mixer=dict(ATTN["mixer"], heads=2, kv_heads=1, dim=64, vdim=200, rot={"base": 5e5, "dims": 64})),
+                     dict(d, mixer={"heads": 3, "kv_heads": 1, "dim": 17, "vdim": 33, "conv": 4})],
+             width=88, vocab=97, streams=2),
+    ]
+    c = cases[case]
+    cfg, w, model = make(c["layers"], width=c["width"], vocab=c["vocab"], streams=c["streams"])
+    ids = toks(75, c["vocab"], seed=60 + case)
+    want = O.forward(cfg, w, ids)
+    eng = engine(model)
+    got = [eng.forward([("a", ids[:41], list(range(41)))]), eng.forward([("a", ids[41:70], list(range(29)))])]
+    got += [eng.forward([("a", [t], [0])]) for t in ids[70:]]
+    assert err(torch.cat(got), want) < TOL32
+
+
+# ---- the engine's own entry point -----------------------------------------------------------------------------------
+def test_greedy_generation_through_the_scheduler():
+    """Six prompts, two slots, small steps: prompts are cut into portions beside decoding sequences, and slots and pages
+    go round.  Every generated token must be the oracle's greedy choice given the same history (ties within rounding)."""
+    cfg, w, model = make(HYBRID, dtype="bfloat16")
+    eng = engine(model, max_tokens=64 * 5, max_seqs=2)
+    prompts = [toks(n, seed=70 + n) for n in (5, 90, 33, 64, 1, 17)]
+    outs = eng.generate(prompts, max_new_tokens=12, step_tokens=40)
+    assert not eng.cache.seqs and len(eng.cache.free_slots) == 2
+    assert eng.cache.allocator.get_num_free_pages() == eng.cache.n_pages
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        ref = O.forward(cfg, w, p + o)
+        for j, tok in enumerate(o):
+            row = ref[len(p) - 1 + j]
+            assert float(row.max() - row[tok]) < 0.15, (len(p), j)
+
+
+def test_sampled_generation_is_reproducible():
+    from proxy_inference_engine_b200.samplers import make_sampler
+    cfg, w, model = make([DELTA, ATTN], dtype="bfloat16")
+    prompts = [toks(9, seed=80), toks(20, seed=81)]
+    a = engine(model).generate(prompts, 8, sampler=make_sampler(temp=0.8, top_p=0.9, seed=3))
+    b = engine(model).generate(prompts, 8, sampler=make_sampler(temp=0.8, top_p=0.9, seed=3))
+    assert a == b and all(0 <= t < 203 for o in a for t in o)
