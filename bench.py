@@ -38,6 +38,10 @@ def parse():
     ap.add_argument("--no-70b", action="store_true", help="N > 1: skip the Llama-3.1-70B tensor-parallel sub-records")
     ap.add_argument("--no-config3", action="store_true", help="skip the 8-bit / batch-32 / paged-KV sub-record (BASELINE configs[2])")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM figure (BASELINE config 4 shapes)")
+    ap.add_argument("--family", default="llama", choices=("llama", "golitar"),
+                    help="golitar: prefill / decode throughput and per-operator rooflines of the Golitar family at --size, "
+                         "beside the quantized Llama path at equal size (its own JSON line; the default workload is untouched)")
+    ap.add_argument("--size", default="1b", help="--family golitar: layer sizes, 1b or 8b")
     return ap.parse_args()
 
 
@@ -659,9 +663,23 @@ def run_reference(a):
     print(json.dumps(line), flush=True)
 
 
+def run_golitar(a):
+    from proxy_inference_engine_b200 import hybrid_bench
+    rec = hybrid_bench.run(a.size, prompt=max(a.prompt, 4096) if a.prompt == 128 else a.prompt, batch=max(a.batch, 4)
+                           if a.batch == 1 else a.batch, steps=min(a.steps, 64), warmup=max(a.warmup, 3), root=ROOT)
+    line = {"metric": "golitar decode tok/s", "value": rec["decode"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
+            "steps": min(a.steps, 64), "warmup": max(a.warmup, 3), "ms_per_step": rec["decode"]["ms_per_step"],
+            "higher_is_better": True, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "gpu_launches": rec["decode"]["launches_per_step"] * min(a.steps, 64), "config": {"model": f"golitar-{a.size}"}}
+    line.update(rec)
+    print(json.dumps(line), flush=True)
+
+
 if __name__ == "__main__":
     args = parse()
-    if args.impl == "reference":
+    if args.family == "golitar":
+        run_golitar(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

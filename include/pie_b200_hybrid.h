@@ -28,6 +28,9 @@ extern "C" {
 int pieh_abi_version(void);
 const char* pieh_last_cuda_error(void);
 unsigned long long pieh_launch_count(void);
+/* non-zero after a tensor-core pipeline gave up a bounded wait (the kernel returned early; its output is invalid).
+ * Synchronises the device. */
+unsigned int pieh_pipeline_error(void);
 
 /* epilogues of pieh_linear */
 enum {

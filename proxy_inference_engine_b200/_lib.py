@@ -164,6 +164,7 @@ HYBRID_SIGNATURES = {
     "pieh_abi_version": (_i, []),
     "pieh_last_cuda_error": (C.c_char_p, []),
     "pieh_launch_count": (C.c_ulonglong, []),
+    "pieh_pipeline_error": (C.c_uint, []),
     "pieh_linear": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _i, _vp]),
     "pieh_embed_streams": (_i, [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp]),
     "pieh_stream_norm": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i, _vp]),

@@ -12,6 +12,17 @@ int status_of(cudaError_t e);   // cudaError_t -> pie_status, remembering the me
 void count_launch(int n = 1);
 int num_sms();
 
+// one pieh_linear call
+struct LinArgs {
+  void* out; long long out_ld;
+  const void* x; long long x_ld;
+  const void* w;
+  const float* bias;
+  int M, N, K, epi;
+  float epi_a;
+  const float* mix; const float* outw; int S;
+};
+
 template <typename T> struct elem;
 template <> struct elem<float> {
   static __device__ __forceinline__ float load(const float* p) { return *p; }

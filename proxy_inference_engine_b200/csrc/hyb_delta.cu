@@ -14,48 +14,57 @@ namespace pieh {
 
 constexpr int kMaxTaps = 8;
 
-__global__ void __launch_bounds__(256) delta_prepare_kernel(float* q, float* k, float* v, float* beta, float* decay,
+// grid (T, 2 G + H): one CTA per token and head-sized unit -- the G heads of q, the G heads of k, the H heads of v
+__global__ void __launch_bounds__(128) delta_prepare_kernel(float* q, float* k, float* v, float* beta, float* decay,
                                                             const float* proj, long long ld, const pieh_delta d,
                                                             const pieh_batch b) {
-  extern __shared__ float ch[];   // conv + silu of the q and k channels of this token
-  const int t = blockIdx.x;
+  __shared__ float red[33];
+  const int t = blockIdx.x, u = blockIdx.y;
   const int i = b.tok_seq[t], start = b.seq_start[i], ctx = b.seq_ctx[i], slot = b.seq_slot[i];
   const int j = t - start;
   const int nq = d.G * d.dk, C = 2 * nq + d.H * d.dv, taps = d.taps;
   const float* hist = d.conv_state + (size_t)slot * (taps - 1) * C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
-    float acc = 0.f;
-    for (int r = 0; r < taps; ++r) {
-      float x;
-      if (r <= j) x = proj[(size_t)(t - r) * ld + c];
-      else {
-        const int back = r - j;   // 1 .. taps - 1 tokens before this step
-        x = ctx - back >= 0 ? hist[(size_t)(taps - 1 - back) * C + c] : 0.f;
+  const bool is_v = u >= 2 * d.G;
+  const int n = is_v ? d.dv : d.dk;
+  const int base = is_v ? 2 * nq + (u - 2 * d.G) * d.dv : u * d.dk;
+  float y[4], ss = 0.f;   // n <= 512
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int c = base + threadIdx.x + 128 * e;
+    y[e] = 0.f;
+    if (threadIdx.x + 128 * e < n) {
+      float acc = 0.f;
+      for (int r = 0; r < taps; ++r) {
+        float x;
+        if (r <= j) x = proj[(size_t)(t - r) * ld + c];
+        else {
+          const int back = r - j;   // 1 .. taps - 1 tokens before this step
+          x = ctx - back >= 0 ? hist[(size_t)(taps - 1 - back) * C + c] : 0.f;
+        }
+        acc = fmaf(d.conv_w[(size_t)c * taps + (taps - 1 - r)], x, acc);
       }
-      acc = fmaf(d.conv_w[(size_t)c * taps + (taps - 1 - r)], x, acc);
+      y[e] = silu_f(acc);
+      ss = fmaf(y[e], y[e], ss);
     }
-    const float y = silu_f(acc);
-    if (c < 2 * nq) ch[c] = y;
-    else v[(size_t)t * d.H * d.dv + (c - 2 * nq)] = y;
   }
-  __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-  for (int hh = warp; hh < 2 * d.G; hh += nw) {   // heads of q, then heads of k
-    const float* src = ch + (size_t)hh * d.dk;
-    float ss = 0.f;
-    for (int c = lane; c < d.dk; c += 32) ss = fmaf(src[c], src[c], ss);
-    ss = warp_sum(ss);
-    float inv = 1.f / sqrtf(ss + 1e-6f);
-    float* dst;
-    if (hh < d.G) { inv *= 1.f / sqrtf((float)d.dk); dst = q + ((size_t)t * d.G + hh) * d.dk; }
-    else dst = k + ((size_t)t * d.G + (hh - d.G)) * d.dk;
-    for (int c = lane; c < d.dk; c += 32) dst[c] = src[c] * inv;
+  float inv = 1.f;
+  float* dst;
+  if (is_v) dst = v + (size_t)t * d.H * d.dv + (base - 2 * nq);
+  else {
+    ss = block_sum(ss, red);
+    inv = 1.f / sqrtf(ss + 1e-6f);
+    if (u < d.G) { inv *= 1.f / sqrtf((float)d.dk); dst = q + (size_t)t * nq + base; }
+    else dst = k + (size_t)t * nq + (base - nq);
   }
-  if (threadIdx.x < d.H) {
-    const int h = threadIdx.x;
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+    if (threadIdx.x + 128 * e < n) dst[threadIdx.x + 128 * e] = y[e] * inv;
+  if (u == 0) {
     const float* row = proj + (size_t)t * ld + C + d.H * d.dv;   // behind the gate columns: b, then a
-    beta[(size_t)t * d.H + h] = 1.f / (1.f + expf(-row[h]));
-    decay[(size_t)t * d.H + h] = expf(-expf(d.A_log[h]) * softplus_f(row[d.H + h] + d.dt_bias[h]));
+    for (int h = threadIdx.x; h < d.H; h += 128) {
+      beta[(size_t)t * d.H + h] = 1.f / (1.f + expf(-row[h]));
+      decay[(size_t)t * d.H + h] = expf(-expf(d.A_log[h]) * softplus_f(row[d.H + h] + d.dt_bias[h]));
+    }
   }
 }
 
@@ -79,11 +88,17 @@ __global__ void conv_advance_kernel(const float* proj, long long ld, const pieh_
 
 constexpr int kScanThreads = 128, kScanChunk = 16;
 
+__device__ __forceinline__ void cp_async_f(float* smem_dst, const float* gsrc, int bytes) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gsrc) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gsrc) : "memory");
+}
+
 template <int RPT>
 __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, const float* q, const float* k, const float* v,
                                                                   const float* beta, const float* decay,
                                                                   const pieh_delta d, const pieh_batch b, int R) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int cols = kScanThreads / R;
   const int h = blockIdx.y, i = blockIdx.z;
   const int hk = h / (d.H / d.G);
@@ -92,63 +107,93 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, cons
   const int j = blockIdx.x * cols + cl;           // column of S (feature of v)
   const bool col_ok = j < d.dv;
   const int dk = d.dk, dv = d.dv;
-  float* ks = sm;                                  // [chunk][dk]
-  float* qs = ks + kScanChunk * dk;                // [chunk][dk]
-  float* vs = qs + kScanChunk * dk;                // [chunk][cols]
-  float* gb = vs + kScanChunk * cols;              // [chunk][2]: decay, beta
+  // two chunk buffers: while the recurrence walks one chunk of tokens, cp.async fills the other
+  const int buf_floats = kScanChunk * (2 * dk + cols + 2);
   float* S_g = d.state + (((size_t)b.seq_slot[i] * d.H + h) * dk) * dv;
   float S[RPT];
 #pragma unroll
   for (int r = 0; r < RPT; ++r) {
-    const int row = rl * RPT + r;
+    const int row = r * R + rl;   // rows are dealt round-robin to the R lanes: lane rl reads bank-adjacent k, q entries
     S[r] = (ctx > 0 && col_ok && row < dk) ? S_g[(size_t)row * dv + j] : 0.f;
   }
-  for (int c0 = 0; c0 < n; c0 += kScanChunk) {
+  const bool vec = (dk & 3) == 0;
+  auto fill = [&](int which, int c0) {
+    float* ks = sm + which * buf_floats;
+    float* qs = ks + kScanChunk * dk;
+    float* vs = qs + kScanChunk * dk;
+    float* gb = vs + kScanChunk * cols;
     const int nc = min(kScanChunk, n - c0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nc * dk; e += kScanThreads) {
-      const int tt = e / dk, r = e - tt * dk;
-      const size_t src = ((size_t)(start + c0 + tt) * d.G + hk) * dk + r;
-      ks[e] = k[src];
-      qs[e] = q[src];
+    if (vec) {
+      const int per = dk >> 2;
+      for (int e = threadIdx.x; e < nc * per; e += kScanThreads) {
+        const int tt = e / per, r = (e - tt * per) << 2;
+        const size_t src = ((size_t)(start + c0 + tt) * d.G + hk) * dk + r;
+        cp_async_f(ks + tt * dk + r, k + src, 16);
+        cp_async_f(qs + tt * dk + r, q + src, 16);
+      }
+    } else {
+      for (int e = threadIdx.x; e < nc * dk; e += kScanThreads) {
+        const int tt = e / dk, r = e - tt * dk;
+        const size_t src = ((size_t)(start + c0 + tt) * d.G + hk) * dk + r;
+        cp_async_f(ks + e, k + src, 4);
+        cp_async_f(qs + e, q + src, 4);
+      }
     }
     for (int e = threadIdx.x; e < nc * cols; e += kScanThreads) {
       const int tt = e / cols, c = e - tt * cols;
-      const int jj = blockIdx.x * cols + c;
-      vs[e] = jj < dv ? v[((size_t)(start + c0 + tt) * d.H + h) * dv + jj] : 0.f;
+      const int jj = min(blockIdx.x * cols + c, dv - 1);
+      cp_async_f(vs + e, v + ((size_t)(start + c0 + tt) * d.H + h) * dv + jj, 4);
     }
     for (int e = threadIdx.x; e < nc; e += kScanThreads) {
-      gb[2 * e] = decay[(size_t)(start + c0 + e) * d.H + h];
-      gb[2 * e + 1] = beta[(size_t)(start + c0 + e) * d.H + h];
+      cp_async_f(gb + 2 * e, decay + (size_t)(start + c0 + e) * d.H + h, 4);
+      cp_async_f(gb + 2 * e + 1, beta + (size_t)(start + c0 + e) * d.H + h, 4);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fill(0, 0);
+  for (int c0 = 0, which = 0; c0 < n; c0 += kScanChunk, which ^= 1) {
+    const int nc = min(kScanChunk, n - c0);
+    if (c0 + kScanChunk < n) {
+      fill(which ^ 1, c0 + kScanChunk);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    const float* ks = sm + which * buf_floats;
+    const float* qs = ks + kScanChunk * dk;
+    const float* vs = qs + kScanChunk * dk;
+    const float* gb = vs + kScanChunk * cols;
     for (int tt = 0; tt < nc; ++tt) {
       const float g = gb[2 * tt], be = gb[2 * tt + 1];
-      const float* kr = ks + tt * dk + rl * RPT;
-      const float* qr = qs + tt * dk + rl * RPT;
-      float kk[RPT], pred = 0.f;
+      const float* kr = ks + tt * dk + rl;
+      const float* qr = qs + tt * dk + rl;
+      float kk[RPT], pp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < RPT; ++r) {
-        kk[r] = rl * RPT + r < dk ? kr[r] : 0.f;
+        kk[r] = r * R + rl < dk ? kr[r * R] : 0.f;
         S[r] *= g;
-        pred = fmaf(S[r], kk[r], pred);
+        pp[r & 3] = fmaf(S[r], kk[r], pp[r & 3]);
       }
+      float pred = (pp[0] + pp[1]) + (pp[2] + pp[3]);
       for (int off = 1; off < R; off <<= 1) pred += __shfl_xor_sync(0xffffffffu, pred, off);
       const float u = be * (vs[tt * cols + cl] - pred);
-      float out = 0.f;
+      float oo[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < RPT; ++r) {
         S[r] = fmaf(kk[r], u, S[r]);
-        out = fmaf(S[r], rl * RPT + r < dk ? qr[r] : 0.f, out);
+        oo[r & 3] = fmaf(S[r], r * R + rl < dk ? qr[r * R] : 0.f, oo[r & 3]);
       }
+      float out = (oo[0] + oo[1]) + (oo[2] + oo[3]);
       for (int off = 1; off < R; off <<= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
       if (rl == 0 && col_ok) o[((size_t)(start + c0 + tt) * d.H + h) * dv + j] = out;
     }
+    __syncthreads();   // everyone is done with this buffer before the next fill overwrites it
   }
   if (col_ok) {
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-      const int row = rl * RPT + r;
+      const int row = r * R + rl;
       if (row < dk) S_g[(size_t)row * dv + j] = S[r];
     }
   }
@@ -172,7 +217,7 @@ __global__ void delta_gate_kernel(OT* out, const float* o, const float* proj, lo
 
 static bool delta_ok(const pieh_delta* d) {
   return d && d->H > 0 && d->G > 0 && d->H % d->G == 0 && d->dk > 0 && d->dv > 0 && d->taps >= 1 && d->taps <= kMaxTaps &&
-         d->dk <= 512 && d->H <= 256;
+         d->dk <= 512 && d->dv <= 512;
 }
 
 }  // namespace pieh
@@ -185,10 +230,8 @@ extern "C" int pieh_delta_prepare(float* q, float* k, float* v, float* beta, flo
   if (!delta_ok(d)) return PIE_EINVAL_SHAPE;
   if (b->T == 0) return PIE_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const size_t smem = (size_t)2 * d->G * d->dk * 4;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   count_launch(2);
-  delta_prepare_kernel<<<b->T, 256, smem, st>>>(q, k, v, beta, decay, proj, ld, *d, *b);
+  delta_prepare_kernel<<<dim3(b->T, 2 * d->G + d->H), 128, 0, st>>>(q, k, v, beta, decay, proj, ld, *d, *b);
   if (d->taps > 1) {
     const int C = 2 * d->G * d->dk + d->H * d->dv;
     conv_advance_kernel<<<dim3((C + 127) / 128, b->n_seq), 128, 0, st>>>(proj, ld, *d, *b);
@@ -205,10 +248,10 @@ extern "C" int pieh_delta_scan(float* o, const float* q, const float* k, const f
   int R = 1;
   while (R * RPT < d->dk) R <<= 1;   // lanes per column, a power of two <= 32
   const int cols = kScanThreads / R;
-  const size_t smem = (size_t)kScanChunk * (2 * d->dk + cols + 2) * 4;
+  const size_t smem = (size_t)2 * kScanChunk * (2 * d->dk + cols + 2) * 4;
   static bool opted = false;
   if (smem > 48 * 1024 && !opted) {
-    cudaFuncSetAttribute(delta_scan_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    cudaFuncSetAttribute(delta_scan_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     opted = true;
   }
   count_launch();

@@ -1,9 +1,9 @@
 // Dense linear layers y = x W^T (+ bias) over unquantized weights, with the epilogues of pie_b200_hybrid.h.
 //
 // Three kernels behind pieh_linear:
-//   * linear_rows_kernel  (M <= 8: decode): a warp per output row streams the weight row once with 16-byte loads and
-//     keeps one fp32 accumulator per activation row -- bound by the weight bytes;
-//   * linear_umma_kernel  (bf16 x bf16, M >= 128, K % 64 == 0: prefill): tcgen05.mma with the fp32 accumulator in
+//   * linear_rows_kernel  (M <= 32: decode): a CTA streams 1, 2 or 4 weight rows once with 16-byte loads, its warps cutting K
+//     between them, one fp32 accumulator per (activation row, weight row) -- bound by the weight bytes;
+//   * linear_umma_kernel  (bf16 x bf16, M > 32, K % 64 == 0: prefill): tcgen05.mma with the fp32 accumulator in
 //     tensor memory, both operands brought into 128B-swizzled K-major shared memory by cp.async (hyb_umma.cu);
 //   * linear_tile_kernel  (everything else, and every fp32 product): 64 x 64 tiles, fp32 multiply-add on the CUDA cores.
 // With bf16 weights the activation is rounded to bf16 first, so the three agree up to the order of the fp32 sums.
@@ -11,15 +11,6 @@
 
 namespace pieh {
 
-struct LinArgs {
-  void* out; long long out_ld;
-  const void* x; long long x_ld;
-  const void* w;
-  const float* bias;
-  int M, N, K, epi;
-  float epi_a;
-  const float* mix; const float* outw; int S;
-};
 
 cudaError_t launch_linear_umma(const LinArgs& a, int out_dtype, cudaStream_t st);   // hyb_umma.cu
 bool linear_umma_ok(const LinArgs& a, int x_dtype, int w_dtype);
@@ -92,7 +83,7 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// M <= 8.  A warp per output row; a lane takes 8 consecutive k per round (16 bytes of bf16, 32 of fp32).
+// M <= 32.  A CTA per R output rows; a lane takes 8 consecutive k per round (16 bytes of bf16, 32 of fp32).
 template <typename T> struct vec8;
 template <> struct vec8<float> {
   static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
@@ -109,33 +100,52 @@ template <> struct vec8<__nv_bfloat16> {
   }
 };
 
-template <typename XT, typename WT, typename OT, int MR>
+template <typename XT, typename WT, typename OT, int MR, int R>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
+  // one CTA per R consecutive output rows; its 8 warps cut K between them and meet in shared memory
+  __shared__ float part[8][MR][R];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n = blockIdx.x * 8 + warp;
-  if (n >= a.N) return;
+  const int n0 = blockIdx.x * R;
   const XT* x = reinterpret_cast<const XT*>(a.x);
-  const WT* w = reinterpret_cast<const WT*>(a.w) + (size_t)n * a.K;
-  float acc[MR];
+  const WT* w = reinterpret_cast<const WT*>(a.w);
+  float acc[MR][R];
 #pragma unroll
-  for (int m = 0; m < MR; ++m) acc[m] = 0.f;
-  for (int k = lane * 8; k < a.K; k += 256) {
-    float wv[8];
-    vec8<WT>::load(w + k, wv);
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[m][r] = 0.f;
+#pragma unroll 2
+  for (int k = (warp * 32 + lane) * 8; k < a.K; k += 2048) {
+    float wv[R][8];
+#pragma unroll
+    for (int r = 0; r < R; ++r) vec8<WT>::load(w + (size_t)min(n0 + r, a.N - 1) * a.K + k, wv[r]);
 #pragma unroll
     for (int m = 0; m < MR; ++m) {
       if (m < a.M) {
         float xv[8];
         vec8<XT>::load(x + (size_t)m * a.x_ld + k, xv);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[m] = fmaf(elem<WT>::round(xv[i]), wv[i], acc[m]);
+        for (int i = 0; i < 8; ++i) {
+          const float xr = sizeof(XT) == sizeof(WT) ? xv[i] : elem<WT>::round(xv[i]);   // already in the product type
+#pragma unroll
+          for (int r = 0; r < R; ++r) acc[m][r] = fmaf(xr, wv[r][i], acc[m][r]);
+        }
       }
     }
   }
 #pragma unroll
-  for (int m = 0; m < MR; ++m) {
-    const float y = warp_sum(acc[m]);
-    if (lane == 0 && m < a.M) lin_store<OT>(a, m, n, y);
+  for (int m = 0; m < MR; ++m)
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float y = warp_sum(acc[m][r]);
+      if (lane == 0) part[warp][m][r] = y;
+    }
+  __syncthreads();
+  for (int e = threadIdx.x; e < MR * R; e += 256) {
+    const int m = e / R, r = e - m * R;
+    float y = 0.f;
+#pragma unroll
+    for (int wp = 0; wp < 8; ++wp) y += part[wp][m][r];
+    if (m < a.M && n0 + r < a.N) lin_store<OT>(a, m, n0 + r, y);
   }
 }
 
@@ -144,11 +154,16 @@ static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
   const bool vec_ok = a.K % 8 == 0 && a.x_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 31) == 0 &&
                       (reinterpret_cast<uintptr_t>(a.w) & 31) == 0;
   count_launch();
-  if (a.M <= 8 && vec_ok) {
-    const int grid = (a.N + 7) / 8;
-    if (a.M <= 1) linear_rows_kernel<XT, WT, OT, 1><<<grid, 256, 0, st>>>(a);
-    else if (a.M <= 4) linear_rows_kernel<XT, WT, OT, 4><<<grid, 256, 0, st>>>(a);
-    else linear_rows_kernel<XT, WT, OT, 8><<<grid, 256, 0, st>>>(a);
+  if (a.M <= 32 && vec_ok) {
+    // rows per CTA: enough to amortise the activation loads, few enough that every SM still gets several CTAs
+    const bool wide = a.N >= 4 * 4 * num_sms();
+#define PIEH_ROWS(MR, R) linear_rows_kernel<XT, WT, OT, MR, R><<<(a.N + R - 1) / R, 256, 0, st>>>(a)
+    if (a.M <= 1) { if (wide) PIEH_ROWS(1, 2); else PIEH_ROWS(1, 1); }
+    else if (a.M <= 4) { if (wide) PIEH_ROWS(4, 4); else PIEH_ROWS(4, 2); }
+    else if (a.M <= 8) { if (wide) PIEH_ROWS(8, 4); else PIEH_ROWS(8, 2); }
+    else if (a.M <= 16) PIEH_ROWS(16, 2);
+    else PIEH_ROWS(32, 2);
+#undef PIEH_ROWS
   } else {
     const dim3 grid((a.N + 63) / 64, (a.M + 63) / 64);
     linear_tile_kernel<XT, WT, OT><<<grid, 256, 0, st>>>(a);

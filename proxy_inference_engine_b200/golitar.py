@@ -266,32 +266,33 @@ class GolitarModel:
         return logits
 
 
-def random_weights(args: GolitarArgs, seed: int = 0) -> dict:
-    """A synthetic checkpoint of this design (bf16 tensors on the CPU): matrices U(-1, 1) / sqrt(in), norm offsets and
-    biases small, stream weights near the plain residual, decays spread over (0, 1)."""
-    g = torch.Generator().manual_seed(seed)
+def random_weights(args: GolitarArgs, seed: int = 0, device="cpu") -> dict:
+    """A synthetic checkpoint of this design (bf16 tensors): matrices U(-1, 1) / sqrt(in), norm offsets and biases
+    small, stream weights near the plain residual, decays spread over (0, 1).  device: where the values are drawn
+    (the CPU stream is the reproducible one the tests use; large benchmark models draw on the GPU)."""
+    g = torch.Generator(device=device).manual_seed(seed)
     bf = torch.bfloat16
-    rnd = lambda *s: torch.rand(s, generator=g) * 2 - 1
+    rnd = lambda *s: torch.rand(s, generator=g, device=device) * 2 - 1
     lin = lambda o, i: (rnd(o, i) / math.sqrt(i)).to(bf)
     S, W = args.streams, args.width
-    w = {"embed": torch.randn((args.vocab, W), generator=g).to(bf), "head": lin(args.vocab, W),
+    w = {"embed": torch.randn((args.vocab, W), generator=g, device=device).to(bf), "head": lin(args.vocab, W),
          "final.norm": (0.1 * rnd(W)).to(bf)}
     for i, cfg in enumerate(args.layers):
         p, m = f"l{i}.", cfg["mixer"]
         subs = ["1"] + (["2"] if cfg.get("mlp") else [])
         for q in subs:
             w[p + "norm" + q] = (0.1 * rnd(W)).to(bf)
-            w[p + f"hc{q}.in"] = (torch.full((S,), 1.0 / S) + 0.1 * rnd(S)).to(bf)
-            w[p + f"hc{q}.out"] = (torch.ones(S) + 0.2 * rnd(S)).to(bf)
-            w[p + f"hc{q}.mix"] = (torch.eye(S) + 0.1 * rnd(S, S)).to(bf)
+            w[p + f"hc{q}.in"] = (1.0 / S + 0.1 * rnd(S)).to(bf)
+            w[p + f"hc{q}.out"] = (1.0 + 0.2 * rnd(S)).to(bf)
+            w[p + f"hc{q}.mix"] = (torch.eye(S, device=device) + 0.1 * rnd(S, S)).to(bf)
         if cfg["type"] == "delta":
             H, G, dk, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m.get("conv") or 1
             for n, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
                 w[p + "mix." + n] = lin(rows, W)
                 if m.get("conv"):
-                    w[p + f"mix.{n}.conv"] = (rnd(rows, taps) / math.sqrt(taps) + torch.eye(taps)[-1]).to(bf)
+                    w[p + f"mix.{n}.conv"] = (rnd(rows, taps) / math.sqrt(taps) + torch.eye(taps, device=device)[-1]).to(bf)
             w[p + "mix.g"], w[p + "mix.b"], w[p + "mix.a"] = lin(H * dv, W), lin(H, W), lin(H, W)
-            w[p + "mix.A_log"] = torch.log(0.5 + 4 * torch.rand(H, generator=g)).to(bf)
+            w[p + "mix.A_log"] = torch.log(0.5 + 4 * torch.rand(H, generator=g, device=device)).to(bf)
             w[p + "mix.dt_bias"] = (rnd(H) - 2.0).to(bf)
             w[p + "mix.norm"] = (1 + 0.1 * rnd(dv)).to(bf)
             w[p + "mix.o"] = lin(W, H * dv)

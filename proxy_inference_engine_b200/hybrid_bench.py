@@ -1,0 +1,225 @@
+"""Throughput of the Golitar family at layer sizes of real models (random weights), beside the quantized Llama path at
+equal width / feed-forward / depth, with every operator of the step timed in place and set against its roofline.
+
+``run(size, ...)`` is what ``bench.py --family golitar`` prints.  Method: one prompt of ``prompt`` tokens goes through
+``HybridEngine.forward`` in portions of ``portion`` rows (prefill tok/s, CUDA events around all portions), then ``batch``
+sequences decode ``steps`` tokens each (decode tok/s).  The per-operator table wraps every library call of one prefill
+portion and one decode step in a CUDA event pair; bytes and flops are the algorithmic ones of the call's shapes, the
+roofline time is max(bytes / measured copy bandwidth, flops / measured bf16 tensor throughput), ``frac`` = roofline time /
+measured time."""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import torch
+
+SIZES = {
+    # width, feed-forward, heads x dims of the delta mixer and of the attention mixer, layers as a pattern string
+    "1b": dict(width=2048, ff=8192, vocab=32000, pattern="dddadddadddadddA", dH=16, dG=16, dk=128, dv=128, aH=16, aG=4,
+               ad=64, adv=128, window=1024, llama=dict(hidden_size=2048, intermediate_size=8192, num_attention_heads=32,
+                                                       num_key_value_heads=8, head_dim=64, vocab_size=32000)),
+    "8b": dict(width=4096, ff=14336, vocab=32000, pattern="dddadddA", dH=32, dG=16, dk=128, dv=128, aH=32, aG=8, ad=64,
+               adv=128, window=2048, llama=dict(hidden_size=4096, intermediate_size=14336, num_attention_heads=32,
+                                                num_key_value_heads=8, head_dim=128, vocab_size=32000)),
+}
+
+
+def golitar_config(size: str) -> dict:
+    s = SIZES[size]
+    layers = []
+    for ch in s["pattern"]:
+        mlp = {"kind": "dense", "ff": s["ff"]}
+        if ch == "d":
+            layers.append({"type": "delta", "mlp": mlp,
+                           "mixer": {"heads": s["dH"], "kv_heads": s["dG"], "dim": s["dk"], "vdim": s["dv"], "conv": 4}})
+        else:
+            layers.append({"type": "attention", "mlp": mlp,
+                           "mixer": {"heads": s["aH"], "kv_heads": s["aG"], "dim": s["ad"], "vdim": s["adv"], "diff": 0.3,
+                                     "scale": s["ad"] ** -0.5, "softcap": 50.0, "mask": {"size": s["window"]},
+                                     "rot": {"base": 1e6, "dims": s["ad"],
+                                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}})
+    return {"architecture": "Golitar", "vocab": s["vocab"], "width": s["width"], "streams": 2, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def _peaks(root):
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+class _Timed:
+    """Wraps the library so that every call is bracketed by CUDA events; cost(name, args) gives (bytes, flops)."""
+
+    def __init__(self, lib):
+        self._lib, self.log, self.on = lib, [], False
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if not name.startswith("pieh_") or name in ("pieh_launch_count", "pieh_pipeline_error"):
+            return fn
+
+        def call(*args):
+            if not self.on:
+                return fn(*args)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn(*args)
+            e1.record()
+            self.log.append((name, args, e0, e1))
+            return r
+        return call
+
+
+def _cost(name, a, model, batch_info):
+    """Algorithmic (bytes, flops, label) of one call from its arguments."""
+    act = 2 if model.act == 0 else 4
+    T, n_seq, ctx = batch_info
+    if name == "pieh_linear":
+        M, N, K, epi = a[9], a[10], a[11], a[12]
+        ob = 4 if a[1] == 1 else 2
+        wb = 4 if a[7] == 1 else 2
+        extra = 2 * model.S * M * N * 4 if epi == 3 else M * N * ob
+        return N * K * wb + M * K * act + extra, 2.0 * M * N * K, f"linear M={M}"
+    if name in ("pieh_stream_norm",):
+        R, S, W = a[8], a[9], a[10]
+        return R * S * W * 4 + R * W * act, 0.0, "stream_norm"
+    if name == "pieh_embed_streams":
+        return a[4] * a[5] * a[6] * 4, 0.0, "embed"
+    if name.startswith("pieh_delta"):
+        d = a[-3]._obj if name != "pieh_delta_gate" else a[6]._obj
+        H, G, dk, dv = d.H, d.G, d.dk, d.dv
+        C = 2 * G * dk + H * dv
+        if name == "pieh_delta_prepare":
+            return T * (C * 2 + 2 * H) * 4, 2.0 * T * C * d.taps, "delta_prepare"
+        if name == "pieh_delta_scan":
+            return n_seq * 2 * H * dk * dv * 4 + T * (2 * G * dk + 2 * H * dv + 2 * H) * 4, 6.0 * T * H * dk * dv, "delta_scan"
+        return T * H * dv * (8 + act), 0.0, "delta_gate"
+    at = a[-3]._obj
+    H, G, d, dv = at.H, at.G, at.d, at.dv
+    if name == "pieh_attn_prepare":
+        return T * ((H + G) * 2 * d * 4 + G * dv * 4 + H * 2 * d * 4 + G * (2 * d + dv) * act), 0.0, "attn_prepare"
+    keys = min(at.window or (ctx + T), ctx + T)
+    per_q = min(keys, ctx + (T // max(n_seq, 1) + 1) / 2) if T > n_seq else keys
+    kv_bytes = n_seq * min(ctx + T // max(n_seq, 1), keys + T // max(n_seq, 1)) * G * (2 * d + dv) * act
+    return kv_bytes + T * H * (2 * d * 4 + dv * act), 2.0 * T * H * per_q * (2 * d + 2 * dv), "attn_run"
+
+
+def _table(timed, model, batch_info, hbm, tfl):
+    agg = {}
+    for name, args, e0, e1 in timed.log:
+        ms = e0.elapsed_time(e1)
+        by, fl, label = _cost(name, args, model, batch_info)
+        r = agg.setdefault(label, {"calls": 0, "us": 0.0, "bytes": 0.0, "flops": 0.0})
+        r["calls"] += 1; r["us"] += ms * 1e3; r["bytes"] += by; r["flops"] += fl
+    for r in agg.values():
+        roof_us = max(r["bytes"] / (hbm * 1e3), r["flops"] / (tfl * 1e6))
+        r["bound"] = "memory" if r["bytes"] / (hbm * 1e3) >= r["flops"] / (tfl * 1e6) else "tensor"
+        r["frac"] = round(roof_us / r["us"], 4) if r["us"] else None
+        r["us"] = round(r["us"], 1)
+        r["gbytes"], r["gflops"] = round(r.pop("bytes") / 1e9, 4), round(r.pop("flops") / 1e9, 2)
+    return agg
+
+
+def run(size="1b", prompt=4096, portion=2048, batch=4, steps=32, warmup=3, root=".", with_llama=True) -> dict:
+    from .engine import HybridEngine
+    from .golitar import GolitarArgs, GolitarModel, random_weights
+
+    cfg = golitar_config(size)
+    args = GolitarArgs.from_dict(cfg)
+    hbm, tfl, src = _peaks(root)
+    t0 = time.time()
+    model = GolitarModel(args, random_weights(args, seed=0, device="cuda"), "cuda", "bfloat16")
+    n_params = sum(l.w.numel() for ly in model.layers for l in ly.values() if hasattr(l, "w")) + model.head.w.numel()
+    timed = _Timed(model.L)
+    model.L = timed
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, args.vocab, (batch, prompt + steps + warmup + 1), generator=g).tolist()
+    eng = HybridEngine(model, max_tokens=batch * (prompt + steps + warmup + 64), max_seqs=batch)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def prefill(sid, row):
+        for at in range(0, prompt, portion):
+            eng.forward([(sid, row[at:at + portion], None)])
+
+    prefill("warm", ids[0]); eng.finish("warm")
+    torch.cuda.synchronize()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for b in range(batch):
+        prefill(b, ids[b])
+    e1.record(); torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1) / batch
+    pos = prompt
+    for _ in range(warmup):
+        eng.forward([(b, [ids[b][pos]], None) for b in range(batch)]); pos += 1
+    torch.cuda.synchronize()
+    e0, e1 = ev(), ev()
+    launches0 = int(timed._lib.pieh_launch_count())
+    e0.record()
+    for _ in range(steps):
+        eng.forward([(b, [ids[b][pos]], None) for b in range(batch)]); pos += 1
+    e1.record(); torch.cuda.synchronize()
+    decode_ms = e0.elapsed_time(e1) / steps
+    launches = (int(timed._lib.pieh_launch_count()) - launches0) // steps
+    # one decode step and one prompt portion with every call timed
+    timed.on = True
+    eng.forward([(b, [ids[b][pos]], None) for b in range(batch)])
+    torch.cuda.synchronize()
+    dec_table = _table(timed, model, (batch, batch, pos), hbm, tfl)
+    timed.log = []
+    eng.finish(0)
+    eng.forward([("p", ids[0][:portion], None)])
+    torch.cuda.synchronize()
+    pre_table = _table(timed, model, (portion, 1, 0), hbm, tfl)
+    timed.on = False
+    out = {"family": "golitar", "size": size, "params": n_params, "layers": SIZES[size]["pattern"], "dtype": "bf16",
+           "data": "synthetic (random weights)", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src},
+           "prefill": {"prompt": prompt, "portion": portion, "ms": round(prefill_ms, 2),
+                       "tok_s": round(prompt / prefill_ms * 1e3, 1)},
+           "decode": {"batch": batch, "context": prompt, "ms_per_step": round(decode_ms, 3),
+                      "tok_s": round(batch / decode_ms * 1e3, 1), "launches_per_step": launches},
+           "kernels_prefill_portion": pre_table, "kernels_decode_step": dec_table,
+           "pipeline_error": int(timed._lib.pieh_pipeline_error()), "setup_s": round(time.time() - t0, 1)}
+    del eng, model
+    torch.cuda.empty_cache()
+    if with_llama:
+        out["llama_equal_size"] = _llama(size, prompt, batch, steps, warmup)
+    return out
+
+
+def _llama(size, prompt, batch, steps, warmup) -> dict:
+    """The quantized Llama path (q4, gs64) at the same width, feed-forward size and depth: whole-prompt prefill through
+    Model.__call__ and graph-replayed decode through DecodeEngine."""
+    from .checkpoint import build_model, random_weights
+    from .decode import DecodeEngine
+    from .llama import ModelArgs
+
+    s = SIZES[size]
+    margs = ModelArgs(num_hidden_layers=len(s["pattern"]), rms_norm_eps=1e-5, rope_theta=500000.0,
+                      max_position_embeddings=131072, tie_word_embeddings=False,
+                      rope_scaling={"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0},
+                      quantization={"group_size": 64, "bits": 4}, **s["llama"])
+    model = build_model(margs, random_weights(margs, seed=0, device="cuda"))
+    eng = DecodeEngine(model, batch=batch, max_context=prompt + steps + warmup + 64)
+    ids = torch.randint(0, margs.vocab_size, (batch, prompt), generator=torch.Generator().manual_seed(1))
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    eng.prefill(ids)
+    torch.cuda.synchronize()
+    e0, e1 = ev(), ev()
+    e0.record(); eng.prefill(ids); e1.record(); torch.cuda.synchronize()
+    prefill_ms = e0.elapsed_time(e1) / batch
+    eng.step(max(warmup, 3))
+    torch.cuda.synchronize()
+    e0, e1 = ev(), ev()
+    e0.record(); eng.step(steps); e1.record(); torch.cuda.synchronize()
+    decode_ms = e0.elapsed_time(e1) / steps
+    return {"model": "llama q4 gs64, same width / ff / depth", "prefill": {"prompt": prompt, "ms": round(prefill_ms, 2),
+                                                                          "tok_s": round(prompt / prefill_ms * 1e3, 1)},
+            "decode": {"batch": batch, "ms_per_step": round(decode_ms, 3), "tok_s": round(batch / decode_ms * 1e3, 1),
+                       "launches_per_step": eng.launches_per_step}}

@@ -113,6 +113,41 @@ def test_linear_kernels_agree_with_a_plain_product():
                 assert err(out, y) < 1e-5, (M, N, K, exact, epi)
 
 
+def test_tensor_core_linear_matches_a_plain_product():
+    """bf16 activations, M >= 64, K a multiple of 64: the tcgen05 kernel, both tile heights, ragged M and N, every epilogue."""
+    import ctypes as C
+    from proxy_inference_engine_b200 import _lib
+    L = _lib.load_hybrid(build_if_missing=True)
+    g = torch.Generator().manual_seed(1)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    for M, N, K in [(64, 256, 64), (130, 300, 192), (300, 77, 128), (1000, 520, 256), (2100, 5000, 64)]:
+        x = torch.randn((M, K), generator=g).to(torch.bfloat16).cuda()
+        wt = (torch.randn((N, K), generator=g) / K ** 0.5).to(torch.bfloat16).cuda()
+        bias = torch.randn((N,), generator=g).cuda()
+        y = x.double().cpu() @ wt.double().cpu().T + bias.double().cpu()
+        for epi, odt in ((0, 1), (1, 0), (2, 1)):
+            out = torch.empty((M, N), dtype=torch.float32 if odt else torch.bfloat16, device="cuda")
+            assert L.pieh_linear(p(out), odt, N, p(x), 0, K, p(wt), 0, p(bias), M, N, K, epi, 5.0, None, None, 0, None) == 0
+            ref = torch.relu(y) ** 2 if epi == 1 else (5.0 * torch.tanh(y / 5.0) if epi == 2 else y)
+            assert err(out.float(), ref) < (1e-5 if odt else 5e-3), (M, N, K, epi)
+        S = 3
+        xs = torch.randn((M, S, N), generator=g).cuda()
+        mix, ow = torch.randn((S, S), generator=g).cuda(), torch.randn((S,), generator=g).cuda()
+        ref = torch.einsum("su,msn->mun", mix.double().cpu(), xs.double().cpu()) + ow.double().cpu()[None, :, None] * y[:, None]
+        assert L.pieh_linear(p(xs), 1, 0, p(x), 0, K, p(wt), 0, p(bias), M, N, K, 3, 0.0, p(mix), p(ow), S, None) == 0
+        assert err(xs.reshape(M, -1), ref.reshape(M, -1)) < 1e-5
+    assert L.pieh_pipeline_error() == 0
+
+
+def test_long_portions_run_on_the_tensor_cores():
+    cfg, w, model = make([dict(DELTA, mlp=FF), dict(ATTN, mlp=FF)], width=128, dtype="bfloat16")
+    ids = toks(200)
+    want = O.forward(cfg, w, ids)
+    eng = engine(model)
+    got = torch.cat([eng.forward([("a", ids[:150], list(range(150)))]), eng.forward([("a", ids[150:], list(range(50)))])])
+    assert err(got, want) < TOL16 and model.L.pieh_pipeline_error() == 0
+
+
 # ---- schedules ------------------------------------------------------------------------------------------------------
 HYBRID = [dict(DELTA, mlp=None), dict(ATTN, mlp=FF), DELTA]
 
