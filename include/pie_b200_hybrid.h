@@ -52,6 +52,9 @@ typedef struct pieh_batch {
   const int32_t* seq_slot; /* [n_seq]  state slot of the sequence             */
   const int32_t* block_table; /* [n_seq, bt_stride] page ids                  */
   int bt_stride;
+  int n_tiles;             /* 64-row query tiles: every sequence's rows cut into runs of <= 64 (0: no tile list)  */
+  const int32_t* tile_seq; /* [n_tiles] sequence of the tile                  */
+  const int32_t* tile_row; /* [n_tiles] first row of the tile                 */
 } pieh_batch;
 
 /* y[m, n] = sum_k x[m, k] w[n, k] (+ bias[n]), fp32 accumulation.  w_dtype bf16: x is rounded to bf16 (if it is not

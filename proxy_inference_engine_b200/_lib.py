@@ -140,7 +140,8 @@ class HybBatch(C.Structure):
     """pieh_batch"""
     _fields_ = [("T", C.c_int), ("n_seq", C.c_int), ("tok_seq", C.c_void_p), ("tok_pos", C.c_void_p),
                 ("seq_start", C.c_void_p), ("seq_len", C.c_void_p), ("seq_ctx", C.c_void_p), ("seq_slot", C.c_void_p),
-                ("block_table", C.c_void_p), ("bt_stride", C.c_int)]
+                ("block_table", C.c_void_p), ("bt_stride", C.c_int), ("n_tiles", C.c_int), ("tile_seq", C.c_void_p),
+                ("tile_row", C.c_void_p)]
 
 
 class HybDelta(C.Structure):

@@ -110,12 +110,19 @@ class BatchDetails:
             acc += m
         tok_seq = [i for i, m in enumerate(self.input_lengths) for _ in range(m)]
         slots = list(self.state_slots) if self.state_slots else [0] * n
-        host = torch.tensor(tok_seq + starts + list(self.input_lengths) + list(self.context_lengths) + slots,
-                            dtype=torch.int32)
+        tile_seq, tile_row = [], []          # runs of <= 64 rows of one sequence: the query tiles of prompt attention
+        for i, (s0, m) in enumerate(zip(starts, self.input_lengths)):
+            for r0 in range(0, m, 64):
+                tile_seq.append(i)
+                tile_row.append(s0 + r0)
+        nt = len(tile_seq)
+        host = torch.tensor(tok_seq + starts + list(self.input_lengths) + list(self.context_lengths) + slots + tile_seq
+                            + tile_row, dtype=torch.int32)
         dev = host.to(self.token_ids.device)
         ptr = lambda off: dev.data_ptr() + 4 * off
         d = HybBatch(T, n, ptr(0), self.positions.data_ptr(), ptr(T), ptr(T + n), ptr(T + 2 * n), ptr(T + 3 * n),
-                     self.consolidated_block_table.data_ptr(), self.consolidated_block_table.stride(0))
+                     self.consolidated_block_table.data_ptr(), self.consolidated_block_table.stride(0), nt,
+                     ptr(T + 4 * n), ptr(T + 4 * n + nt))
         return d, (dev, self.positions, self.consolidated_block_table)
 
     def token_block_table(self) -> torch.Tensor:

@@ -96,7 +96,10 @@ def test_ragged_descriptor_layout():
     d, keep = b.hybrid_descriptor()
     flat = keep[0].tolist()
     assert (d.T, d.n_seq, d.bt_stride) == (4, 2, 2)
-    assert flat == [0, 0, 0, 1] + [0, 3] + [3, 1] + [70, 0] + [2, 0]
+    assert flat == [0, 0, 0, 1] + [0, 3] + [3, 1] + [70, 0] + [2, 0] + [0, 1] + [0, 3] and d.n_tiles == 2
+    big = BatchDetails.build([("x", list(range(130)), 0, [1, 2, 3], 0), ("y", [1], 5, [4], 1)], device="cpu")
+    d2, keep2 = big.hybrid_descriptor()
+    assert d2.n_tiles == 4 and keep2[0].tolist()[-8:] == [0, 0, 0, 1, 0, 64, 128, 130]
     assert b.consolidated_block_table.tolist() == [[3, 9], [4, 0]]
 
 

@@ -222,13 +222,13 @@ def test_a_freed_slot_does_not_leak_its_state():
 
 
 # ---- edges ----------------------------------------------------------------------------------------------------------
-def _peaky(window):
+def _peaky(window, gain=4.0):
     """One attention layer whose scores are large, so that a single key inside or outside the window shows."""
     a = copy.deepcopy(ATTN)
     a["mixer"]["mask"] = {"size": window}
     a["mixer"]["scale"] = 1.0
     a["mixer"]["softcap"] = 40.0
-    big = lambda t: t.float() * 4.0
+    big = lambda t: t.float() * gain
     return [a], {"l0.mix.q.norm": big, "l0.mix.k.norm": big}
 
 
@@ -256,6 +256,103 @@ def test_window_edge_in_prompt_and_in_decoding(window, n):
             for t in range(last - 3, last + 1):
                 d = eng.forward([("d", [ids[t]], [0])])
             assert err(p, ref[None]) < TOL32 and err(d, ref[None]) < TOL32, (back, seen)
+
+
+@pytest.mark.parametrize("d,dv,window", [(64, 64, 9), (64, 128, 64), (32, 128, 65), (32, 64, 100), (64, 128, 200), (64, 64, 0)])
+def test_prompt_tiles_on_tensor_cores(d, dv, window):
+    """bf16, head sizes the tile kernel takes: whole prompts, portions that start inside a page and inside a tile, a
+    decoding sequence in the same step, against the restatement; and the window's edge must show."""
+    layers, edit = _peaky(window or 7, gain=2.5)   # bf16 keys: moderate peaks, looser bound
+    tol = 5e-2
+    layers[0]["mixer"].update(dim=d, vdim=dv, heads=4, kv_heads=2, rot={"base": 1e4, "dims": d // 2})
+    if not window:
+        layers[0]["mixer"].pop("mask")
+    cfg, w, model = make(layers, edit=edit, dtype="bfloat16", width=64)
+    n = 330
+    ids, other = toks(n, seed=21), toks(40, seed=22)
+    want, want_o = O.forward(cfg, w, ids), O.forward(cfg, w, other)
+    eng = engine(model)
+    assert err(eng.forward([("w", ids, list(range(n)))]), want) < tol
+    got = [eng.forward([("p", ids[:37], list(range(37)))])]
+    eng.forward([("o", other[:39], [])])
+    mixed = eng.forward([("p", ids[37:237], list(range(200))), ("o", other[39:], [0])])    # 200 rows + one decode row
+    got += [mixed[:200], eng.forward([("p", ids[237:], list(range(n - 237)))])]
+    assert err(torch.cat(got), want) < tol and err(mixed[200:], want_o[39:]) < tol
+
+
+def _attention_op(q, k, v, window, portions, act=torch.bfloat16, lam=0.4, cap=30.0, scale=0.5):
+    """pieh_attn_prepare + pieh_attn_run on given q [T, H, 2, d], k [T, G, 2, d], v [T, G, dv] (no norm, no rotation),
+    one sequence fed in the given portions over scattered pages; returns [T, H, dv] float."""
+    import ctypes as C
+    from proxy_inference_engine_b200 import _lib
+    from proxy_inference_engine_b200.ragged import BatchDetails
+    L = _lib.load_hybrid(build_if_missing=True)
+    T, H, _, d = q.shape
+    G, dv = k.shape[1], v.shape[2]
+    proj = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], 1).float().cuda().contiguous()
+    n_pages = (T + 63) // 64 + 3
+    pages = list(range(n_pages - 1, 1, -1))                       # descending ids: a page table that is not the identity
+    kp = torch.full((n_pages, 64, G, 2 * d), 7.0, dtype=act, device="cuda")     # stale finite contents everywhere
+    vp = torch.full((n_pages, 64, G, dv), -3.0, dtype=act, device="cuda")
+    code = 0 if act == torch.bfloat16 else 1
+    at = _lib.HybAttn(H, G, d, dv, 0, None, None, None, 1e-6, scale, cap, window, lam, 0.8, kp.data_ptr(), vp.data_ptr(), code)
+    outs, ctx = [], 0
+    for n in portions:
+        b = BatchDetails.build([("s", [0] * n, ctx, pages, 0)], device="cuda")
+        desc, keep = b.hybrid_descriptor()
+        qo = torch.empty((n, H, 2, d), dtype=torch.float32, device="cuda")
+        out = torch.empty((n, H * dv), dtype=act, device="cuda")
+        part = proj[ctx:ctx + n].contiguous()
+        p = lambda t: C.c_void_p(t.data_ptr())
+        assert L.pieh_attn_prepare(p(qo), p(part), part.stride(0), C.byref(at), C.byref(desc), None) == 0
+        assert L.pieh_attn_run(p(out), code, p(qo), C.byref(at), C.byref(desc), None) == 0
+        torch.cuda.synchronize()
+        outs.append(out.float().view(n, H, dv))
+        ctx += n
+    return torch.cat(outs).cpu()
+
+
+def _attention_ref(q, k, v, window, lam=0.4, cap=30.0, scale=0.5):
+    rep = q.shape[1] // k.shape[1]
+    kk, vv = k.double().repeat_interleave(rep, 1), v.double().repeat_interleave(rep, 1)
+    m = [O.windowed_softmax_attention(q.double()[:, :, i], kk[:, :, i], vv, scale, cap, window) for i in (0, 1)]
+    return O.unit_rms(m[0] - lam * m[1], 1e-6) * 0.8
+
+
+@pytest.mark.parametrize("act", [torch.bfloat16, torch.float32], ids=["tiles-bf16", "rows-fp32"])
+@pytest.mark.parametrize("d,dv", [(64, 128), (32, 64)])
+@pytest.mark.parametrize("window", [5, 64, 65, 128, 130, 300])
+def test_attention_operator_window_edge_with_a_dominant_key(act, d, dv, window):
+    """One key per probe scores far above the rest and carries a value unlike the others: the probe row's output is that
+    value exactly when the key is the oldest one inside the window, and is not when it is one step further back.  Probes
+    sit at tile and page borders; prompt portions start inside pages; bf16 runs the tensor-core tiles, fp32 the row kernel."""
+    g = torch.Generator().manual_seed(window)
+    T, H, G = 400, 4, 2
+    q = 0.1 * torch.randn((T, H, 2, d), generator=g)
+    k = 0.1 * torch.randn((T, G, 2, d), generator=g)
+    v = torch.randn((T, G, dv), generator=g)
+    plan = [(window - 1, window - 1), (T - 1, window), (255, window - 1), (320, window)]
+    plants = {}                                                # probe row -> planted key: just inside / just outside
+    for r, back in plan:
+        if r < T and r - back >= 0 and r not in plants:
+            plants[r] = r - back
+    for r, j in plants.items():
+        q[r, :, :, :] = 0
+        q[r, :, 0, 3] = 8.0                                    # map 1 of the probe row looks along feature 3
+        k[j, :, 0, 3] = 8.0
+        v[j] = 4.0 + torch.arange(dv)[None] * 0.01            # a value row that is easy to recognise
+    sees = lambda r: any(0 <= r - j < window for j in plants.values())
+    q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))
+    ref = _attention_ref(q, k, v, window)
+    tol = 3e-2 if act == torch.bfloat16 else 1e-4
+    for portions in ([T], [37, 200, 163], [64, 64, 272]):
+        got = _attention_op(q, k, v, window, portions, act)
+        assert err(got.reshape(T, -1), ref.reshape(T, -1)) < tol, portions
+    flat = lambda r: float(ref[r].std(-1).mean())             # a row dominated by the planted value is almost constant
+    edge_in = [r for r, j in plants.items() if r - j == window - 1]
+    edge_out = [r for r, j in plants.items() if r - j == window and not sees(r)]
+    assert edge_in and all(flat(r) < 0.2 for r in edge_in)
+    assert edge_out and all(flat(r) > 0.5 for r in edge_out)
 
 
 def test_no_window_no_rotation_no_caps():
@@ -357,3 +454,44 @@ def test_sampled_generation_is_reproducible():
     a = engine(model).generate(prompts, 8, sampler=make_sampler(temp=0.8, top_p=0.9, seed=3))
     b = engine(model).generate(prompts, 8, sampler=make_sampler(temp=0.8, top_p=0.9, seed=3))
     assert a == b and all(0 <= t < 203 for o in a for t in o)
+
+
+def test_checkpoint_on_disk_through_the_command_line(tmp_path):
+    """config.json + model.safetensors -> registry -> bin/trace_run (two steps, a sequence ended and its slot re-used)
+    and `python -m proxy_inference_engine_b200 generate`."""
+    import json, os, subprocess, sys
+    import numpy as np
+    from safetensors.torch import save_file
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, w, model = make([DELTA, dict(ATTN, mlp=FF)], dtype="float32")
+    mdir, out = tmp_path / "m", tmp_path / "o"
+    mdir.mkdir()
+    save_file({k: v.contiguous() for k, v in w.items()}, str(mdir / "model.safetensors"))
+    (mdir / "config.json").write_text(json.dumps(cfg))
+    a, b = toks(70, seed=90), toks(9, seed=91)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": [0, 65]}, {"id": "b", "tokens": b, "want": [8]}],
+              "end": ["b"]},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[66:], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "c", "tokens": b[:4], "want": [3]}, {"id": "a", "tokens": [a[0]], "want": [0]}],
+              "end": ["a", "c"]}]
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(mdir), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "192", "--max-seqs", "2"], input="\n".join(json.dumps(x) for x in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not (out / "1.f32").exists()
+    ra, rb = O.forward(cfg, w, a + [a[0]]), O.forward(cfg, w, b)
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(3, -1).copy())
+    got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, -1).copy())
+    assert err(got0, torch.stack([ra[0], ra[65], rb[8]])) < TOL32
+    assert err(got2, torch.stack([rb[3], ra[70]])) < TOL32
+    g = subprocess.run([sys.executable, "-m", "proxy_inference_engine_b200", "generate", "--model", str(mdir), "--prompt-ids",
+                        ",".join(map(str, b)), "--max-new-tokens", "5", "--dtype", "float32"], cwd=root, capture_output=True,
+                       text=True, timeout=600)
+    assert g.returncode == 0, g.stderr[-2000:]
+    rec = json.loads(g.stdout.strip().splitlines()[-1])
+    assert rec["prompt_ids"] == b and len(rec["generated_ids"]) == 5
+    ref = O.forward(cfg, w, b + rec["generated_ids"])
+    for jj, tok in enumerate(rec["generated_ids"]):
+        row = ref[len(b) - 1 + jj]
+        assert float(row.max() - row[tok]) < 0.15
