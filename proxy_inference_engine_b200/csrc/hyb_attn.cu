@@ -4,7 +4,7 @@
 // attn_prepare_kernel  per token: RMS norm of every (head, map) of q and k with a shared plain weight, rotation of adjacent
 //                      feature pairs of the first rot_dims features (angle = position x frequency, evaluated in double),
 //                      k and v written to the sequence's page at the token's position
-// attn_run_kernel      one CTA per (token, query head): 4 warps take 32-key blocks of the window in turn, a lane scores
+// attn_run_kernel      one CTA per (token, query head): 8 warps take 32-key blocks of the window in turn, a lane scores
 //                      one key for both maps, the warp keeps an online softmax per map and accumulates p V with the lanes
 //                      spread over the value features; the warps merge through shared memory
 // attn_tile_kernel     prompt portions over bf16 pages: 64-row query tiles on mma.sync (below)
@@ -68,27 +68,48 @@ __global__ void __launch_bounds__(128) attn_prepare_kernel(float* q_out, const f
   for (int c = threadIdx.x; c < a.G * a.dv; c += blockDim.x) elem<KT>::store(vp + c, vsrc[c]);
 }
 
+constexpr int kRunWarps = 8;
+
+template <typename T> struct kv8;   // 8 consecutive cache elements as floats
+template <> struct kv8<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+template <> struct kv8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+  }
+};
+
 template <typename KT, typename OT, int NV>
-__global__ void __launch_bounds__(128) attn_run_kernel(OT* out, const float* q, const pieh_attn a, const pieh_batch b) {
-  extern __shared__ float sm[];
+__global__ void __launch_bounds__(kRunWarps * 32) attn_run_kernel(OT* out, const float* q, const pieh_attn a,
+                                                                  const pieh_batch b) {
+  extern __shared__ __align__(16) float sm[];
   __shared__ float red[33];
+  constexpr int NW = kRunWarps, NTH = kRunWarps * 32;
   const int t = blockIdx.x / a.H, h = blockIdx.x - t * a.H;
   const int g = h / (a.H / a.G);
   const int i = b.tok_seq[t], p = b.tok_pos[t];
   const int d = a.d, dv = a.dv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* qs = sm;                  // [2][d]
-  float* mg = qs + 2 * d;          // [4 warps][2 maps][dv + 2]: acc, m, l
-  for (int c = threadIdx.x; c < 2 * d; c += 128) qs[c] = q[((size_t)t * a.H + h) * 2 * d + c];
+  float* mg = qs + 2 * d;          // [warps][2 maps][dv + 2]: acc, m, l
+  for (int c = threadIdx.x; c < 2 * d; c += NTH) qs[c] = q[((size_t)t * a.H + h) * 2 * d + c];
   __syncthreads();
   const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
   const int32_t* table = b.block_table + (size_t)i * b.bt_stride;
   const KT* kpool = reinterpret_cast<const KT*>(a.k_pages);
   const KT* vpool = reinterpret_cast<const KT*>(a.v_pages);
+  const bool vec = (d & 7) == 0;   // rows of 2 d elements then start on 16-byte boundaries
   float m1 = -1e30f, m2 = -1e30f, l1 = 0.f, l2 = 0.f, acc1[NV], acc2[NV];
 #pragma unroll
   for (int x = 0; x < NV; ++x) acc1[x] = acc2[x] = 0.f;
-  for (int base = lo + warp * 32; base <= p; base += 128) {
+  for (int base = lo + warp * 32; base <= p; base += NW * 32) {
     const int j = base + lane;
     const bool ok = j <= p;
     long long slot = 0;
@@ -97,9 +118,20 @@ __global__ void __launch_bounds__(128) attn_run_kernel(OT* out, const float* q, 
       slot = (long long)table[j / kPage] * kPage + j % kPage;
       const KT* kr = kpool + ((size_t)slot * a.G + g) * 2 * d;
       float d1 = 0.f, d2 = 0.f;
-      for (int c = 0; c < d; ++c) {
-        d1 = fmaf(qs[c], elem<KT>::load(kr + c), d1);
-        d2 = fmaf(qs[d + c], elem<KT>::load(kr + d + c), d2);
+      if (vec) {
+#pragma unroll 4
+        for (int c = 0; c < d; c += 8) {
+          float k1[8], k2[8];
+          kv8<KT>::load(kr + c, k1);
+          kv8<KT>::load(kr + d + c, k2);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { d1 = fmaf(qs[c + e], k1[e], d1); d2 = fmaf(qs[d + c + e], k2[e], d2); }
+        }
+      } else {
+        for (int c = 0; c < d; ++c) {
+          d1 = fmaf(qs[c], elem<KT>::load(kr + c), d1);
+          d2 = fmaf(qs[d + c], elem<KT>::load(kr + d + c), d2);
+        }
       }
       s1 = d1 * a.scale; s2 = d2 * a.scale;
       if (a.softcap > 0.f) { s1 = a.softcap * tanhf(s1 / a.softcap); s2 = a.softcap * tanhf(s2 / a.softcap); }
@@ -112,20 +144,31 @@ __global__ void __launch_bounds__(128) attn_run_kernel(OT* out, const float* q, 
     m1 = n1; m2 = n2;
 #pragma unroll
     for (int x = 0; x < NV; ++x) { acc1[x] *= c1; acc2[x] *= c2; }
-    const int cnt = min(32, p - base + 1);
-    for (int kk = 0; kk < cnt; ++kk) {
-      const float w1 = __shfl_sync(0xffffffffu, p1, kk), w2 = __shfl_sync(0xffffffffu, p2, kk);
-      const long long sl = __shfl_sync(0xffffffffu, slot, kk);
-      const KT* vr = vpool + ((size_t)sl * a.G + g) * dv;
+    // all 32 keys of the block, four at a time with their loads issued together: a key past the row's position has
+    // weight 0 and slot 0 (a valid, finite row), so it adds nothing
+#pragma unroll 1
+    for (int k0 = 0; k0 < 32; k0 += 4) {
+      if (base + k0 > p) break;
+      float w1[4], w2[4], vv[4][NV];
 #pragma unroll
-      for (int x = 0; x < NV; ++x) {
-        const int c = lane + 32 * x;
-        if (c < dv) {
-          const float vv = elem<KT>::load(vr + c);
-          acc1[x] = fmaf(w1, vv, acc1[x]);
-          acc2[x] = fmaf(w2, vv, acc2[x]);
+      for (int u = 0; u < 4; ++u) {
+        w1[u] = __shfl_sync(0xffffffffu, p1, k0 + u);
+        w2[u] = __shfl_sync(0xffffffffu, p2, k0 + u);
+        const long long sl = __shfl_sync(0xffffffffu, slot, k0 + u);
+        const KT* vr = vpool + ((size_t)sl * a.G + g) * dv;
+#pragma unroll
+        for (int x = 0; x < NV; ++x) {
+          const int c = lane + 32 * x;
+          vv[u][x] = c < dv ? elem<KT>::load(vr + c) : 0.f;
         }
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int x = 0; x < NV; ++x) {
+          acc1[x] = fmaf(w1[u], vv[u][x], acc1[x]);
+          acc2[x] = fmaf(w2[u], vv[u][x], acc2[x]);
+        }
     }
   }
   float* mine = mg + (size_t)warp * 2 * (dv + 2);
@@ -136,39 +179,29 @@ __global__ void __launch_bounds__(128) attn_run_kernel(OT* out, const float* q, 
   }
   if (lane == 0) { mine[dv] = m1; mine[dv + 1] = l1; mine[2 * dv + 2] = m2; mine[2 * dv + 3] = l2; }
   __syncthreads();
-  float ssq = 0.f;
-  float ov[(NV + 3) / 4];   // features this thread owns: c = threadIdx.x + 128 * y
-#pragma unroll
-  for (int y = 0; y < (NV + 3) / 4; ++y) {
-    const int c = threadIdx.x + 128 * y;
-    ov[y] = 0.f;
-    if (c < dv) {
-      float res[2];
-      for (int mp = 0; mp < 2; ++mp) {
-        float M = -1e30f;
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, mg[(size_t)(w * 2 + mp) * (dv + 2) + dv]);
-        float L = 0.f, A = 0.f;
-        for (int w = 0; w < 4; ++w) {
-          const float* src = mg + (size_t)(w * 2 + mp) * (dv + 2);
-          const float f = expf(src[dv] - M);
-          L = fmaf(src[dv + 1], f, L);
-          A = fmaf(src[c], f, A);
-        }
-        res[mp] = A / L;
+  // feature c = threadIdx.x (dv <= 256 = threads): merge the warps' partial softmaxes, combine the maps
+  const int c = threadIdx.x;
+  float ov = 0.f;
+  if (c < dv) {
+    float res[2];
+    for (int mp = 0; mp < 2; ++mp) {
+      float M = -1e30f;
+      for (int w = 0; w < NW; ++w) M = fmaxf(M, mg[(size_t)(w * 2 + mp) * (dv + 2) + dv]);
+      float L = 0.f, A = 0.f;
+      for (int w = 0; w < NW; ++w) {
+        const float* src = mg + (size_t)(w * 2 + mp) * (dv + 2);
+        const float f = expf(src[dv] - M);
+        L = fmaf(src[dv + 1], f, L);
+        A = fmaf(src[c], f, A);
       }
-      ov[y] = res[0] - a.lambda * res[1];
-      ssq = fmaf(ov[y], ov[y], ssq);
+      res[mp] = A / L;
     }
+    ov = res[0] - a.lambda * res[1];
   }
-  ssq = block_sum(ssq, red);
+  const float ssq = block_sum(ov * ov, red);
   const float inv = a.out_scale / sqrtf(ssq / (float)dv + a.eps);
-#pragma unroll
-  for (int y = 0; y < (NV + 3) / 4; ++y) {
-    const int c = threadIdx.x + 128 * y;
-    if (c < dv) elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, ov[y] * inv);
-  }
+  if (c < dv) elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, ov * inv);
 }
-
 
 // ---- prompt portions on the tensor cores ---------------------------------------------------------------------------
 // A CTA of 4 warps owns one 64-row query tile (consecutive positions of ONE sequence) of one query head; key tiles are
@@ -291,7 +324,7 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(__nv_bfloat16* out, cons
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           float v = s[n][e] * a.scale;
-          if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+          if (a.softcap > 0.f) v = a.softcap * (1.f - __fdividef(2.f, __expf(2.f * v / a.softcap) + 1.f));   // tanh, abs error ~1e-7
           const int key = k + (e & 1), pr = e < 2 ? p0 : p1, wl = e < 2 ? w0 : w1;
           s[n][e] = (key <= pr && key >= wl) ? v * kLog2e : -INFINITY;
         }
@@ -402,13 +435,13 @@ static bool attn_ok(const pieh_attn* a) {
 
 template <typename KT, typename OT>
 static cudaError_t launch_run(OT* out, const float* q, const pieh_attn& a, const pieh_batch& b, cudaStream_t st) {
-  const size_t smem = ((size_t)2 * a.d + 8 * (a.dv + 2)) * 4;
+  const size_t smem = ((size_t)2 * a.d + 2 * kRunWarps * (a.dv + 2)) * 4;
   const unsigned grid = (unsigned)b.T * a.H;
-  const int nv = (a.dv + 31) / 32;
-  if (nv <= 1) attn_run_kernel<KT, OT, 1><<<grid, 128, smem, st>>>(out, q, a, b);
-  else if (nv <= 2) attn_run_kernel<KT, OT, 2><<<grid, 128, smem, st>>>(out, q, a, b);
-  else if (nv <= 4) attn_run_kernel<KT, OT, 4><<<grid, 128, smem, st>>>(out, q, a, b);
-  else attn_run_kernel<KT, OT, 8><<<grid, 128, smem, st>>>(out, q, a, b);
+  const int nv = (a.dv + 31) / 32, nth = kRunWarps * 32;
+  if (nv <= 1) attn_run_kernel<KT, OT, 1><<<grid, nth, smem, st>>>(out, q, a, b);
+  else if (nv <= 2) attn_run_kernel<KT, OT, 2><<<grid, nth, smem, st>>>(out, q, a, b);
+  else if (nv <= 4) attn_run_kernel<KT, OT, 4><<<grid, nth, smem, st>>>(out, q, a, b);
+  else attn_run_kernel<KT, OT, 8><<<grid, nth, smem, st>>>(out, q, a, b);
   return cudaGetLastError();
 }
 

@@ -17,11 +17,78 @@ import torch
 from .ragged import BatchDetails
 
 
+class _DecodeGraph:
+    """One captured decode step for n sequences of one token each (the launch-bound case): tokens, positions, the
+    per-sequence descriptor and the block table live in ONE device buffer that a single copy from pinned host memory
+    refills before every replay; the model step underneath is the same ``model.step``."""
+
+    def __init__(self, engine, n: int):
+        from ._lib import HybBatch
+        self.n, self.W = n, engine.cache.n_pages
+        W, dev = self.W, engine.device
+        self.host = torch.zeros(9 * n + n * W, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros_like(self.host, device=dev)
+        self.copied = torch.cuda.Event()
+        d = self.dev
+        table = d[9 * n:].view(n, W)
+        ptr = lambda off: d.data_ptr() + 4 * off
+        # layout: tokens | positions | row->sequence | first row | rows | context | slot | tile sequence | tile row | table
+        self.batch = BatchDetails(d[0:n], d[n:2 * n], list(range(n)), [1] * n, [0] * n, table, 0, n, n, [0] * n)
+        desc = HybBatch(n, n, ptr(2 * n), ptr(n), ptr(3 * n), ptr(4 * n), ptr(5 * n), ptr(6 * n), table.data_ptr(), W, n,
+                        ptr(7 * n), ptr(8 * n))
+        self.batch._static_descriptor = (desc, (d,))
+        self.rows = torch.arange(n, dtype=torch.int32, device=dev)
+        h = self.host
+        h[2 * n:3 * n] = torch.arange(n)
+        h[3 * n:4 * n] = torch.arange(n)
+        h[4 * n:5 * n] = 1
+        h[7 * n:8 * n] = torch.arange(n)
+        h[8 * n:9 * n] = torch.arange(n)
+        self.graph = None
+        self.engine = engine
+
+    def run(self, seqs):
+        """seqs: [(tokens [1], context, pages, slot)] in batch order -> logits [n, vocab] (a static tensor)."""
+        n, W, h = self.n, self.W, self.host
+        self.copied.synchronize()
+        for i, (tok, ctx, pages, slot) in enumerate(seqs):
+            h[i], h[n + i], h[5 * n + i], h[6 * n + i] = tok[0], ctx, ctx, slot
+            row = 9 * n + i * W
+            h[row: row + len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        self.dev.copy_(h, non_blocking=True)
+        self.copied.record()
+        model, cache = self.engine.model, self.engine.cache
+        if self.graph is None:
+            model.step(self.batch, cache, rows=self.rows)     # first use: opts kernels into their shared memory; the
+            torch.cuda.synchronize()                           # state it advanced is re-written by the captured run
+            self._rewind(seqs)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.logits = model.step(self.batch, cache, rows=self.rows)
+            self.graph = g
+            self._rewind(seqs)
+        self.graph.replay()
+        return self.logits
+
+    def _rewind(self, seqs):
+        """Undo the recurrent-state advance of a warm-up / capture pass (the pages are simply overwritten again)."""
+        for saved, layer in zip(self._saved, self.engine.cache.layers):
+            for k, v in saved.items():
+                layer[k].copy_(v)
+
+    def snapshot(self):
+        self._saved = [{k: v.clone() for k, v in layer.items() if k in ("state", "conv")} for layer in self.engine.cache.layers]
+
+
 class HybridEngine:
-    def __init__(self, model, max_tokens: int, max_seqs: int = 4):
+    def __init__(self, model, max_tokens: int, max_seqs: int = 4, use_graph: bool = True):
+        """use_graph: steps that are one token for every sequence replay a captured CUDA graph (one per batch size);
+        anything else -- prompt portions, mixed steps -- launches the operators directly."""
         self.model = model
         self.cache = model.make_cache(max_tokens, max_seqs)
         self.device = model.device
+        self.use_graph = use_graph and str(self.device).startswith("cuda")
+        self._graphs = {}
 
     # ---- one step ----------------------------------------------------------------------------------
     def forward(self, entries, trace=None) -> torch.Tensor:
@@ -43,6 +110,20 @@ class HybridEngine:
                     raise ValueError(f"sequence {sid}: wanted row {w} outside its {len(toks)} tokens")
             rows += [row0 + w for w in want]
             row0 += len(toks)
+        if self.use_graph and all(len(toks) == 1 for _, toks, *_ in seqs) and hasattr(self.model, "layers"):
+            n = len(seqs)
+            dg = self._graphs.get(n)
+            if dg is None:
+                dg = self._graphs[n] = _DecodeGraph(self, n)
+            if dg.graph is None:
+                dg.snapshot()
+            logits = dg.run([(toks, ctx, pages, slot) for _, toks, ctx, pages, slot in seqs])
+            for sid, toks, *_ in seqs:
+                self.cache.seqs[sid]["length"] += 1
+            if not rows:
+                return logits[:0]
+            # the graph writes its logits into one fixed tensor: hand out a copy
+            return logits.clone() if rows == list(range(n)) else logits[torch.tensor(rows, device=self.device)]
         batch = BatchDetails.build(seqs, device=self.device)
         # with nothing wanted the head still needs a row: take the last and drop the result
         idx = torch.tensor(rows if rows else [row0 - 1], dtype=torch.int32).to(self.device)

@@ -126,7 +126,7 @@ def _table(timed, model, batch_info, hbm, tfl):
     return agg
 
 
-def run(size="1b", prompt=4096, portion=2048, batch=4, steps=32, warmup=3, root=".", with_llama=True) -> dict:
+def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=".", with_llama=True) -> dict:
     from .engine import HybridEngine
     from .golitar import GolitarArgs, GolitarModel, random_weights
 
@@ -160,16 +160,17 @@ def run(size="1b", prompt=4096, portion=2048, batch=4, steps=32, warmup=3, root=
         eng.forward([(b, [ids[b][pos]], None) for b in range(batch)]); pos += 1
     torch.cuda.synchronize()
     e0, e1 = ev(), ev()
-    launches0 = int(timed._lib.pieh_launch_count())
     e0.record()
     for _ in range(steps):
         eng.forward([(b, [ids[b][pos]], None) for b in range(batch)]); pos += 1
     e1.record(); torch.cuda.synchronize()
     decode_ms = e0.elapsed_time(e1) / steps
-    launches = (int(timed._lib.pieh_launch_count()) - launches0) // steps
-    # one decode step and one prompt portion with every call timed
+    # one decode step (launched directly, not replayed from the captured graph) and one prompt portion, every call timed
+    eng.use_graph = False
     timed.on = True
+    launches0 = int(timed._lib.pieh_launch_count())
     eng.forward([(b, [ids[b][pos]], None) for b in range(batch)])
+    launches = int(timed._lib.pieh_launch_count()) - launches0      # kernels in the captured step
     torch.cuda.synchronize()
     dec_table = _table(timed, model, (batch, batch, pos), hbm, tfl)
     timed.log = []
@@ -183,7 +184,8 @@ def run(size="1b", prompt=4096, portion=2048, batch=4, steps=32, warmup=3, root=
            "prefill": {"prompt": prompt, "portion": portion, "ms": round(prefill_ms, 2),
                        "tok_s": round(prompt / prefill_ms * 1e3, 1)},
            "decode": {"batch": batch, "context": prompt, "ms_per_step": round(decode_ms, 3),
-                      "tok_s": round(batch / decode_ms * 1e3, 1), "launches_per_step": launches},
+                      "tok_s": round(batch / decode_ms * 1e3, 1), "launches_per_step": launches,
+                      "cuda_graph": True},
            "kernels_prefill_portion": pre_table, "kernels_decode_step": dec_table,
            "pipeline_error": int(timed._lib.pieh_pipeline_error()), "setup_s": round(time.time() - t0, 1)}
     del eng, model

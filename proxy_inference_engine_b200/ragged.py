@@ -103,6 +103,8 @@ class BatchDetails:
         """The step as libpie_b200_hybrid.so reads it (pieh_batch): per-row sequence index and position, per-sequence
         first row / rows / context / state slot, and the block table.  One host-to-device copy; returns (struct, keepalive)."""
         from ._lib import HybBatch
+        if getattr(self, "_static_descriptor", None) is not None:   # a captured decode step: fixed buffers, refilled in place
+            return self._static_descriptor
         n, T = len(self.sequence_ids), self.total_tokens_in_step
         starts, acc = [], 0
         for m in self.input_lengths:

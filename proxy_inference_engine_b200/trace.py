@@ -42,7 +42,7 @@ def main(argv=None) -> int:
         print("trace_run needs a CUDA device (there is no CPU path)", file=sys.stderr)
         return 2
     model = load_model(a.model, device="cuda", dtype=a.dtype)
-    eng = HybridEngine(model, max_tokens=a.max_tokens, max_seqs=a.max_seqs)
+    eng = HybridEngine(model, max_tokens=a.max_tokens, max_seqs=a.max_seqs, use_graph=False)   # a replay is not a hot loop
     os.makedirs(a.out, exist_ok=True)
     for line in sys.stdin:
         line = line.strip()
