@@ -36,11 +36,11 @@ def golitar_config(size: str) -> dict:
                            "mixer": {"heads": s["dH"], "kv_heads": s["dG"], "dim": s["dk"], "vdim": s["dv"], "conv": 4}})
         else:
             layers.append({"type": "attention", "mlp": mlp,
-                           "mixer": {"heads": s["aH"], "kv_heads": s["aG"], "dim": s["ad"], "vdim": s["adv"], "diff": 0.3,
-                                     "scale": s["ad"] ** -0.5, "softcap": 50.0, "mask": {"size": s["window"]},
-                                     "rot": {"base": 1e6, "dims": s["ad"],
-                                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}})
-    return {"architecture": "Golitar", "vocab": s["vocab"], "width": s["width"], "streams": 2, "norm": {"eps": 1e-6},
+                           "mixer": {"heads": s["aH"], "kv_heads": s["aG"], "dim": s["ad"], "vdim": s["adv"], "diff": 0.25,
+                                     "scale": s["ad"] ** -0.5, "softcap": 40.0, "mask": {"size": s["window"]},
+                                     "rot": {"base": 5e5, "dims": s["ad"],
+                                             "scaling": {"factor": 4.0, "low": 1.0, "high": 2.0, "original": 4096}}}})
+    return {"architecture": "Golitar", "vocab": s["vocab"], "width": s["width"], "streams": 2, "norm": {"eps": 1e-5},
             "logit_softcap": 30.0, "layers": layers}
 
 
