@@ -31,6 +31,9 @@ unsigned long long pieh_launch_count(void);
 /* non-zero after a tensor-core pipeline gave up a bounded wait (the kernel returned early; its output is invalid).
  * Synchronises the device. */
 unsigned int pieh_pipeline_error(void);
+/* on: every operator is launched as a programmatic dependent of the launch before it on its stream (its blocks may become
+ * resident early and wait at their top); captured into CUDA graphs as such.  Off by default. */
+void pieh_set_pdl(int on);
 
 /* epilogues of pieh_linear */
 enum {

@@ -166,6 +166,7 @@ HYBRID_SIGNATURES = {
     "pieh_last_cuda_error": (C.c_char_p, []),
     "pieh_launch_count": (C.c_ulonglong, []),
     "pieh_pipeline_error": (C.c_uint, []),
+    "pieh_set_pdl": (None, [_i]),
     "pieh_linear": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _i, _vp]),
     "pieh_embed_streams": (_i, [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp]),
     "pieh_stream_norm": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _f, _f, _i, _i, _i, _vp]),

@@ -19,6 +19,7 @@ template <typename KT>
 __global__ void __launch_bounds__(128) attn_prepare_kernel(float* q_out, const float* proj, long long ld, const pieh_attn a,
                                                            const pieh_batch b) {
   extern __shared__ float cs[];   // [rot_dims / 2][2]: cos, sin of this token's angles
+  pdl_sync();
   const int t = blockIdx.x;
   const int i = b.tok_seq[t], p = b.tok_pos[t];
   for (int f = threadIdx.x; f < a.rot_dims / 2; f += blockDim.x) {
@@ -92,6 +93,7 @@ __global__ void __launch_bounds__(kRunWarps * 32) attn_run_kernel(OT* out, const
   extern __shared__ __align__(16) float sm[];
   __shared__ float red[33];
   constexpr int NW = kRunWarps, NTH = kRunWarps * 32;
+  pdl_sync();
   const int t = blockIdx.x / a.H, h = blockIdx.x - t * a.H;
   const int g = h / (a.H / a.G);
   const int i = b.tok_seq[t], p = b.tok_pos[t];
@@ -239,6 +241,7 @@ __global__ void __launch_bounds__(128) attn_tile_kernel(__nv_bfloat16* out, cons
   constexpr int KROWB = 2 * D * 2, VROWB = DV * 2;
   constexpr int KTILE = 64 * KROWB, VTILE = 64 * VROWB;
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_sync();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
   const int tile = blockIdx.x, h = blockIdx.y;
   const int i = b.tile_seq[tile], row0 = b.tile_row[tile];
@@ -415,8 +418,7 @@ static cudaError_t launch_tile(__nv_bfloat16* out, const float* q, const pieh_at
     if (e != cudaSuccess) return e;
     configured |= 1ull << (dev & 63);
   }
-  attn_tile_kernel<D, DV><<<dim3(b.n_tiles, a.H), 128, smem, st>>>(out, q, a, b);
-  return cudaGetLastError();
+  return launch_k(attn_tile_kernel<D, DV>, dim3(b.n_tiles, a.H), dim3(128), smem, st, out, q, a, b);
 }
 
 // the tile kernel serves steps that are mostly prompt portions, over bf16 pages, at the head sizes it is built for
@@ -438,11 +440,10 @@ static cudaError_t launch_run(OT* out, const float* q, const pieh_attn& a, const
   const size_t smem = ((size_t)2 * a.d + 2 * kRunWarps * (a.dv + 2)) * 4;
   const unsigned grid = (unsigned)b.T * a.H;
   const int nv = (a.dv + 31) / 32, nth = kRunWarps * 32;
-  if (nv <= 1) attn_run_kernel<KT, OT, 1><<<grid, nth, smem, st>>>(out, q, a, b);
-  else if (nv <= 2) attn_run_kernel<KT, OT, 2><<<grid, nth, smem, st>>>(out, q, a, b);
-  else if (nv <= 4) attn_run_kernel<KT, OT, 4><<<grid, nth, smem, st>>>(out, q, a, b);
-  else attn_run_kernel<KT, OT, 8><<<grid, nth, smem, st>>>(out, q, a, b);
-  return cudaGetLastError();
+  if (nv <= 1) return launch_k(attn_run_kernel<KT, OT, 1>, dim3(grid), dim3(nth), smem, st, out, q, a, b);
+  if (nv <= 2) return launch_k(attn_run_kernel<KT, OT, 2>, dim3(grid), dim3(nth), smem, st, out, q, a, b);
+  if (nv <= 4) return launch_k(attn_run_kernel<KT, OT, 4>, dim3(grid), dim3(nth), smem, st, out, q, a, b);
+  return launch_k(attn_run_kernel<KT, OT, 8>, dim3(grid), dim3(nth), smem, st, out, q, a, b);
 }
 
 }  // namespace pieh
@@ -456,7 +457,7 @@ extern "C" int pieh_attn_prepare(float* q_out, const float* proj, long long ld, 
   if (b->T == 0) return PIE_OK;
   const size_t smem = (size_t)(a->rot_dims + 2) * 4;
   count_launch();
-  PIEH_DISPATCH_DTYPE(a->kv_dtype, KT, (attn_prepare_kernel<KT><<<b->T, 128, smem, (cudaStream_t)stream>>>(q_out, proj, ld, *a, *b)));
+  PIEH_DISPATCH_DTYPE(a->kv_dtype, KT, launch_k(attn_prepare_kernel<KT>, dim3(b->T), dim3(128), smem, (cudaStream_t)stream, q_out, proj, ld, *a, *b));
   return status_of(cudaGetLastError());
 }
 

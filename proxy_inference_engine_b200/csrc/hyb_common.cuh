@@ -11,6 +11,31 @@ namespace pieh {
 int status_of(cudaError_t e);   // cudaError_t -> pie_status, remembering the message
 void count_launch(int n = 1);
 int num_sms();
+bool pdl_enabled();   // pieh_set_pdl: launch every step operator as a programmatic dependent of the one before it
+
+// Top of every step kernel.  Launched as a programmatic dependent, a grid may become resident while the grid before it is
+// still draining: it lets ITS dependents queue up at once and then waits until everything earlier in the stream has
+// completed and is visible.  Every kernel of a step does this, so completion stays transitive along the stream.
+// Launched the ordinary way both instructions do nothing.
+__device__ __forceinline__ void pdl_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // one pieh_linear call
 struct LinArgs {

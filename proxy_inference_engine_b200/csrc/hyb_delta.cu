@@ -19,6 +19,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* q, float* k, 
                                                             const float* proj, long long ld, const pieh_delta d,
                                                             const pieh_batch b) {
   __shared__ float red[33];
+  pdl_sync();
   const int t = blockIdx.x, u = blockIdx.y;
   const int i = b.tok_seq[t], start = b.seq_start[i], ctx = b.seq_ctx[i], slot = b.seq_slot[i];
   const int j = t - start;
@@ -69,6 +70,7 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(float* q, float* k, 
 }
 
 __global__ void conv_advance_kernel(const float* proj, long long ld, const pieh_delta d, const pieh_batch b) {
+  pdl_sync();
   const int i = blockIdx.y;
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   const int C = 2 * d.G * d.dk + d.H * d.dv, taps = d.taps;
@@ -99,6 +101,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, cons
                                                                   const float* beta, const float* decay,
                                                                   const pieh_delta d, const pieh_batch b, int R) {
   extern __shared__ __align__(16) float sm[];
+  pdl_sync();
   const int cols = kScanThreads / R;
   const int h = blockIdx.y, i = blockIdx.z;
   const int hk = h / (d.H / d.G);
@@ -202,6 +205,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, cons
 template <typename OT>
 __global__ void delta_gate_kernel(OT* out, const float* o, const float* proj, long long ld, long long gate_off,
                                   const pieh_delta d, int T) {
+  pdl_sync();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= T * d.H) return;
   const int t = w / d.H, h = w - t * d.H;
@@ -231,10 +235,10 @@ extern "C" int pieh_delta_prepare(float* q, float* k, float* v, float* beta, flo
   if (b->T == 0) return PIE_OK;
   cudaStream_t st = (cudaStream_t)stream;
   count_launch(2);
-  delta_prepare_kernel<<<dim3(b->T, 2 * d->G + d->H), 128, 0, st>>>(q, k, v, beta, decay, proj, ld, *d, *b);
+  launch_k(delta_prepare_kernel, dim3(b->T, 2 * d->G + d->H), dim3(128), 0, st, q, k, v, beta, decay, proj, ld, *d, *b);
   if (d->taps > 1) {
     const int C = 2 * d->G * d->dk + d->H * d->dv;
-    conv_advance_kernel<<<dim3((C + 127) / 128, b->n_seq), 128, 0, st>>>(proj, ld, *d, *b);
+    launch_k(conv_advance_kernel, dim3((C + 127) / 128, b->n_seq), dim3(128), 0, st, proj, ld, *d, *b);
   }
   return status_of(cudaGetLastError());
 }
@@ -257,9 +261,8 @@ extern "C" int pieh_delta_scan(float* o, const float* q, const float* k, const f
     opted = true;
   }
   count_launch();
-  delta_scan_kernel<RPT><<<dim3((d->dv + cols - 1) / cols, d->H, b->n_seq), kScanThreads, smem, (cudaStream_t)stream>>>(
-      o, q, k, v, beta, decay, *d, *b, R);
-  return status_of(cudaGetLastError());
+  return status_of(launch_k(delta_scan_kernel<RPT>, dim3((d->dv + cols - 1) / cols, d->H, b->n_seq), dim3(kScanThreads), smem,
+                            (cudaStream_t)stream, o, q, k, v, beta, decay, *d, *b, R));
 }
 
 extern "C" int pieh_delta_gate(void* out, int out_dtype, const float* o, const float* proj, long long ld,
@@ -269,7 +272,6 @@ extern "C" int pieh_delta_gate(void* out, int out_dtype, const float* o, const f
   if (T == 0) return PIE_OK;
   const long long warps = (long long)T * d->H;
   count_launch();
-  PIEH_DISPATCH_DTYPE(out_dtype, OT, (delta_gate_kernel<OT><<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-                                          (OT*)out, o, proj, ld, gate_off, *d, T)));
+  PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(delta_gate_kernel<OT>, dim3((unsigned)((warps + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, (OT*)out, o, proj, ld, gate_off, *d, T));
   return status_of(cudaGetLastError());
 }

@@ -39,6 +39,7 @@ template <typename XT, typename WT, typename OT>
 __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 4], Ws[BK][BN + 4];
+  pdl_sync();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const XT* x = reinterpret_cast<const XT*>(a.x);
@@ -104,6 +105,7 @@ template <typename XT, typename WT, typename OT, int MR, int R>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
   // one CTA per R consecutive output rows; its 8 warps cut K between them and meet in shared memory
   __shared__ float part[8][MR][R];
+  pdl_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * R;
   const XT* x = reinterpret_cast<const XT*>(a.x);
@@ -154,10 +156,11 @@ static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
   const bool vec_ok = a.K % 8 == 0 && a.x_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 31) == 0 &&
                       (reinterpret_cast<uintptr_t>(a.w) & 31) == 0;
   count_launch();
+  cudaError_t e = cudaSuccess;
   if (a.M <= 32 && vec_ok) {
     // rows per CTA: enough to amortise the activation loads, few enough that every SM still gets several CTAs
     const bool wide = a.N >= 4 * 4 * num_sms();
-#define PIEH_ROWS(MR, R) linear_rows_kernel<XT, WT, OT, MR, R><<<(a.N + R - 1) / R, 256, 0, st>>>(a)
+#define PIEH_ROWS(MR, R) e = launch_k(linear_rows_kernel<XT, WT, OT, MR, R>, dim3((a.N + R - 1) / R), dim3(256), 0, st, a)
     if (a.M <= 1) { if (wide) PIEH_ROWS(1, 2); else PIEH_ROWS(1, 1); }
     else if (a.M <= 4) { if (wide) PIEH_ROWS(4, 4); else PIEH_ROWS(4, 2); }
     else if (a.M <= 8) { if (wide) PIEH_ROWS(8, 4); else PIEH_ROWS(8, 2); }
@@ -166,9 +169,9 @@ static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
 #undef PIEH_ROWS
   } else {
     const dim3 grid((a.N + 63) / 64, (a.M + 63) / 64);
-    linear_tile_kernel<XT, WT, OT><<<grid, 256, 0, st>>>(a);
+    e = launch_k(linear_tile_kernel<XT, WT, OT>, grid, dim3(256), 0, st, a);
   }
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace pieh

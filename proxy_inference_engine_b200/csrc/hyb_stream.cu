@@ -11,6 +11,8 @@ namespace pieh {
 
 static std::atomic<unsigned long long> g_launches{0};
 static thread_local char g_err[256] = "";
+static std::atomic<int> g_pdl{0};
+bool pdl_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 int status_of(cudaError_t e) {
   if (e == cudaSuccess) return PIE_OK;
@@ -30,6 +32,7 @@ int num_sms() {
 
 template <typename ET>
 __global__ void embed_streams_kernel(float* xs, const ET* table, const int32_t* tokens, int S, int W, int vocab) {
+  pdl_sync();
   const int t = blockIdx.x;
   int id = tokens[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -46,6 +49,7 @@ __global__ void stream_norm_kernel(OT* out, const float* xs, const int32_t* rows
                                    float unit_offset, float eps, int S, int W) {
   extern __shared__ float row[];
   __shared__ float red[33];
+  pdl_sync();
   const int r = blockIdx.x;
   const int t = rows ? rows[r] : r;
   const float* src = xs + (size_t)t * S * W;
@@ -64,6 +68,7 @@ __global__ void stream_norm_kernel(OT* out, const float* xs, const int32_t* rows
 
 __global__ void stream_update_kernel(float* xs, const float* y, const float* mix, const float* outw, int S, int W,
                                      long long n) {
+  pdl_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;   // over T * W
   if (i >= n) return;
   const long long t = i / W;
@@ -86,6 +91,7 @@ using namespace pieh;
 extern "C" int pieh_abi_version(void) { return 1; }
 extern "C" const char* pieh_last_cuda_error(void) { return g_err; }
 extern "C" unsigned long long pieh_launch_count(void) { return g_launches.load(); }
+extern "C" void pieh_set_pdl(int on) { g_pdl.store(on ? 1 : 0); }
 
 extern "C" int pieh_embed_streams(float* xs, const void* table, int table_dtype, const int32_t* tokens, int T, int S, int W,
                                   int vocab, void* stream) {
@@ -94,7 +100,7 @@ extern "C" int pieh_embed_streams(float* xs, const void* table, int table_dtype,
   if (T == 0) return PIE_OK;
   cudaStream_t st = (cudaStream_t)stream;
   count_launch();
-  PIEH_DISPATCH_DTYPE(table_dtype, ET, (embed_streams_kernel<ET><<<T, 256, 0, st>>>(xs, (const ET*)table, tokens, S, W, vocab)));
+  PIEH_DISPATCH_DTYPE(table_dtype, ET, launch_k(embed_streams_kernel<ET>, dim3(T), dim3(256), 0, st, xs, (const ET*)table, tokens, S, W, vocab));
   return status_of(cudaGetLastError());
 }
 
@@ -110,8 +116,7 @@ extern "C" int pieh_stream_norm(void* out, int out_dtype, const float* xs, const
     cudaFuncSetAttribute(stream_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
   count_launch();
-  PIEH_DISPATCH_DTYPE(out_dtype, OT, (stream_norm_kernel<OT><<<R, 256, smem, st>>>((OT*)out, xs, rows, in_w, norm_w,
-                                                                                    unit_offset, eps, S, W)));
+  PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(stream_norm_kernel<OT>, dim3(R), dim3(256), smem, st, (OT*)out, xs, rows, in_w, norm_w, unit_offset, eps, S, W));
   return status_of(cudaGetLastError());
 }
 
@@ -122,6 +127,6 @@ extern "C" int pieh_stream_update(float* xs, const float* y, const float* mix, c
   if (T == 0) return PIE_OK;
   const long long n = (long long)T * W;
   count_launch();
-  stream_update_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(xs, y, mix, outw, S, W, n);
+  launch_k(stream_update_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, xs, y, mix, outw, S, W, n);
   return status_of(cudaGetLastError());
 }

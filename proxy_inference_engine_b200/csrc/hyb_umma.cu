@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
   __shared__ __align__(8) uint64_t full_bar[S], empty_bar[S], accum_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  pdl_sync();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smA = base, smB = base + S * A_STAGE;
