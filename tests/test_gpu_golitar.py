@@ -113,6 +113,96 @@ def test_linear_kernels_agree_with_a_plain_product():
                 assert err(out, y) < 1e-5, (M, N, K, exact, epi)
 
 
+def test_stream_operators_alone():
+    """pieh_stream_norm (weighted stream sum, RMS norm, offset weight, row gather) and pieh_stream_update against the
+    restatement's hyper_step, at stream counts 1, 3 and 8 and a width that is not a multiple of the block."""
+    import ctypes as C
+    from proxy_inference_engine_b200 import _lib
+    L = _lib.load_hybrid(build_if_missing=True)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    g = torch.Generator().manual_seed(4)
+    for S, W, T in ((1, 72, 5), (3, 300, 9), (8, 64, 2)):
+        xs = torch.randn((T, S, W), generator=g)
+        hc = {"h.in": torch.randn((S,), generator=g), "h.out": torch.randn((S,), generator=g),
+              "h.mix": torch.randn((S, S), generator=g)}
+        nw, y = 0.2 * torch.randn((W,), generator=g), torch.randn((T, W), generator=g)
+        seen = {}
+
+        def sub(u):
+            seen["normed"] = O.norm_centered(u, nw.double(), 1e-5)
+            return y.double()
+        want = O.hyper_step(xs.double().permute(1, 0, 2), hc, "h.", sub).permute(1, 0, 2)
+        rows = torch.tensor([T - 1, 0], dtype=torch.int32).cuda()
+        xd, out = xs.cuda().contiguous(), torch.empty((2, W), dtype=torch.float32, device="cuda")
+        assert L.pieh_stream_norm(p(out), 1, p(xd), p(rows), p(hc["h.in"].cuda()), p(nw.cuda()), 1.0, 1e-5, 2, S, W, None) == 0
+        assert err(out, seen["normed"][[T - 1, 0]]) < 1e-5
+        assert L.pieh_stream_update(p(xd), p(y.cuda()), p(hc["h.mix"].cuda().contiguous()), p(hc["h.out"].cuda()), T, S, W, None) == 0
+        assert err(xd.reshape(T, -1), want.reshape(T, -1)) < 1e-5
+
+
+@pytest.mark.parametrize("H,G,dk,dv,taps", [(2, 1, 16, 16, 4), (3, 3, 40, 24, 2), (4, 2, 130, 70, 1), (1, 1, 300, 8, 5)])
+def test_delta_operators_alone(H, G, dk, dv, taps):
+    """pieh_delta_prepare / _scan / _gate fed with given projections (no matrix products), against the restatement's
+    delta mixer with selector matrices: whole sequences, single tokens, uneven portions, two sequences interleaved in one
+    step, and slots that hold another sequence's state when a new one starts."""
+    import ctypes as C
+    from proxy_inference_engine_b200 import _lib
+    from proxy_inference_engine_b200.ragged import BatchDetails
+    L = _lib.load_hybrid(build_if_missing=True)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    g = torch.Generator().manual_seed(dk)
+    nq, nv = G * dk, H * dv
+    P = 2 * nq + 2 * nv + 2 * H
+    sel = torch.eye(P)
+    w = {"q": sel[:nq], "k": sel[nq:2 * nq], "v": sel[2 * nq:2 * nq + nv], "g": sel[2 * nq + nv:2 * nq + 2 * nv],
+         "b": sel[2 * nq + 2 * nv:2 * nq + 2 * nv + H], "a": sel[2 * nq + 2 * nv + H:], "o": torch.eye(nv),
+         "A_log": torch.log(0.2 + torch.rand(H, generator=g)), "dt_bias": torch.randn(H, generator=g) - 1.0,
+         "norm": 1 + 0.1 * torch.randn(dv, generator=g)}
+    if taps > 1:
+        for n, rows in (("q", nq), ("k", nq), ("v", nv)):
+            w[n + ".conv"] = torch.randn((rows, taps), generator=g) / taps ** 0.5
+    m = {"heads": H, "kv_heads": G, "dim": dk, "vdim": dv}
+    seqs = {"a": torch.randn((61, P), generator=g), "b": torch.randn((23, P), generator=g)}
+    want = {k: O.delta_mixer(v.double(), {"x." + n: t for n, t in w.items()}, "x.", m, 1e-5) for k, v in seqs.items()}
+    C_ = 2 * nq + nv
+    conv_w = (torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]]) if taps > 1 else torch.ones((C_, 1))).cuda().contiguous()
+    state = torch.full((3, H, dk, dv), 9.0, device="cuda")                     # slots start full of someone else's state
+    hist = torch.full((3, max(taps - 1, 1), C_), -7.0, device="cuda")
+    d = _lib.HybDelta(H, G, dk, dv, taps, conv_w.data_ptr(), w["A_log"].cuda().data_ptr(), w["dt_bias"].cuda().data_ptr(),
+                      w["norm"].cuda().data_ptr(), 1e-5, hist.data_ptr(), state.data_ptr())
+    keep = [w["A_log"].cuda(), w["dt_bias"].cuda(), w["norm"].cuda()]
+    d.A_log, d.dt_bias, d.out_norm = (t.data_ptr() for t in keep)
+
+    def step(parts):
+        """parts: [(name, rows lo..hi, slot)] -> outputs per part"""
+        b = BatchDetails.build([(n, [0] * (hi - lo), lo, [0], slot) for n, lo, hi, slot in parts], device="cuda")
+        desc, ka = b.hybrid_descriptor()
+        proj = torch.cat([seqs[n][lo:hi] for n, lo, hi, _ in parts]).cuda().contiguous()
+        T = proj.shape[0]
+        f = lambda *sh: torch.empty(sh, dtype=torch.float32, device="cuda")
+        q, k, v, be, de, o, out = f(T, G, dk), f(T, G, dk), f(T, H, dv), f(T, H), f(T, H), f(T, H, dv), f(T, nv)
+        assert L.pieh_delta_prepare(p(q), p(k), p(v), p(be), p(de), p(proj), P, C.byref(d), C.byref(desc), None) == 0
+        assert L.pieh_delta_scan(p(o), p(q), p(k), p(v), p(be), p(de), C.byref(d), C.byref(desc), None) == 0
+        assert L.pieh_delta_gate(p(out), 1, p(o), p(proj), P, 2 * nq + nv, C.byref(d), T, None) == 0
+        torch.cuda.synchronize()
+        res, at = [], 0
+        for n, lo, hi, _ in parts:
+            res.append(out[at:at + hi - lo].cpu())
+            at += hi - lo
+        return res
+
+    assert err(step([("a", 0, 61, 0)])[0], want["a"]) < 1e-4                                   # whole, slot 0
+    got = torch.cat([step([("a", t, t + 1, 1)])[0] for t in range(61)])                          # token by token, slot 1
+    assert err(got, want["a"]) < 1e-4
+    # slot 0 now holds a's final state: b starts there from zero, interleaved with a restarting in slot 2
+    cuts_a, cuts_b = [0, 5, 6, 26, 61], [0, 2, 3, 20, 23]
+    ga, gb = [], []
+    for i in range(4):
+        ra, rb = step([("b", cuts_b[i], cuts_b[i + 1], 0), ("a", cuts_a[i], cuts_a[i + 1], 2)])[::-1]
+        ga.append(ra); gb.append(rb)
+    assert err(torch.cat(ga), want["a"]) < 1e-4 and err(torch.cat(gb), want["b"]) < 1e-4
+
+
 def test_tensor_core_linear_matches_a_plain_product():
     """bf16 activations, M >= 64, K a multiple of 64: the tcgen05 kernel, both tile heights, ragged M and N, every epilogue."""
     import ctypes as C
