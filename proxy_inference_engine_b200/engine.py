@@ -12,6 +12,7 @@ step underneath, also usable on its own: the caller names which sequences advanc
 schedule, speculative verification, scoring)."""
 from __future__ import annotations
 
+import gc
 import os
 
 import torch
@@ -47,7 +48,7 @@ class _DecodeGraph:
         h[7 * n:8 * n] = torch.arange(n)
         h[8 * n:9 * n] = torch.arange(n)
         self.graph = None
-        self.engine = engine
+        self.model, self.cache, self.use_pdl = engine.model, engine.cache, engine.use_pdl   # no reference back to the engine
 
     def run(self, seqs):
         """seqs: [(tokens [1], context, pages, slot)] in batch order -> logits [n, vocab] (a static tensor)."""
@@ -59,23 +60,28 @@ class _DecodeGraph:
             h[row: row + len(pages)] = torch.tensor(pages, dtype=torch.int32)
         self.dev.copy_(h, non_blocking=True)
         self.copied.record()
-        model, cache = self.engine.model, self.engine.cache
+        model, cache = self.model, self.cache
         if self.graph is None:
             # PIE_HYBRID_PDL=1: the captured launches become programmatic dependents of one another (a kernel's blocks
             # are resident while the kernel before it drains and wait at their top, pieh_set_pdl).  Measured on B200 at
             # the 1b layer sizes, batch 4: 1.70 ms per step against 1.67 ms without -- the step is bound by the kernels'
             # own dependent latencies, not by the gaps between them -- so it is off unless asked for
-            pdl = getattr(model.L, "pieh_set_pdl", None) if self.engine.use_pdl else None
+            pdl = getattr(model.L, "pieh_set_pdl", None) if self.use_pdl else None
             try:
                 if pdl:
                     pdl(1)
                 model.step(self.batch, cache, rows=self.rows)     # first use: opts kernels into their shared memory; the
                 torch.cuda.synchronize()                           # state it advanced is put back before the capture
                 self._rewind(seqs)
+                # nothing may be destroyed while the stream captures (an older engine's graph freed by the cycle collector
+                # in the middle of it invalidates the capture): collect now, and keep the collector off until the end
+                gc.collect()
+                gc.disable()
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     self.logits = model.step(self.batch, cache, rows=self.rows)
             finally:
+                gc.enable()
                 if pdl:
                     pdl(0)
             self.graph = g
@@ -85,12 +91,12 @@ class _DecodeGraph:
 
     def _rewind(self, seqs):
         """Undo the recurrent-state advance of a warm-up / capture pass (the pages are simply overwritten again)."""
-        for saved, layer in zip(self._saved, self.engine.cache.layers):
+        for saved, layer in zip(self._saved, self.cache.layers):
             for k, v in saved.items():
                 layer[k].copy_(v)
 
     def snapshot(self):
-        self._saved = [{k: v.clone() for k, v in layer.items() if k in ("state", "conv")} for layer in self.engine.cache.layers]
+        self._saved = [{k: v.clone() for k, v in layer.items() if k in ("state", "conv")} for layer in self.cache.layers]
 
 
 class HybridEngine:
