@@ -153,6 +153,8 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, cons
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
+  float out_prev = 0.f;   // this lane's share of the last token's read-out, not yet summed over the R lanes
+  int row_prev = -1;
   fill(0, 0);
   for (int c0 = 0, which = 0; c0 < n; c0 += kScanChunk, which ^= 1) {
     const int nc = min(kScanChunk, n - c0);
@@ -179,7 +181,13 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, cons
         pp[r & 3] = fmaf(S[r], kk[r], pp[r & 3]);
       }
       float pred = (pp[0] + pp[1]) + (pp[2] + pp[3]);
-      for (int off = 1; off < R; off <<= 1) pred += __shfl_xor_sync(0xffffffffu, pred, off);
+      // the read-out of the PREVIOUS token is reduced over the R lanes together with this token's prediction: two
+      // independent shuffle chains instead of two in a row on the recurrence's critical path
+      for (int off = 1; off < R; off <<= 1) {
+        pred += __shfl_xor_sync(0xffffffffu, pred, off);
+        out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
+      }
+      if (row_prev >= 0 && rl == 0 && col_ok) o[((size_t)row_prev * d.H + h) * dv + j] = out_prev;
       const float u = be * (vs[tt * cols + cl] - pred);
       float oo[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -187,12 +195,13 @@ __global__ void __launch_bounds__(kScanThreads) delta_scan_kernel(float* o, cons
         S[r] = fmaf(kk[r], u, S[r]);
         oo[r & 3] = fmaf(S[r], r * R + rl < dk ? qr[r * R] : 0.f, oo[r & 3]);
       }
-      float out = (oo[0] + oo[1]) + (oo[2] + oo[3]);
-      for (int off = 1; off < R; off <<= 1) out += __shfl_xor_sync(0xffffffffu, out, off);
-      if (rl == 0 && col_ok) o[((size_t)(start + c0 + tt) * d.H + h) * dv + j] = out;
+      out_prev = (oo[0] + oo[1]) + (oo[2] + oo[3]);
+      row_prev = start + c0 + tt;
     }
     __syncthreads();   // everyone is done with this buffer before the next fill overwrites it
   }
+  for (int off = 1; off < R; off <<= 1) out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
+  if (row_prev >= 0 && rl == 0 && col_ok) o[((size_t)row_prev * d.H + h) * dv + j] = out_prev;
   if (col_ok) {
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
