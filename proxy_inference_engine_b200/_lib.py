@@ -197,15 +197,19 @@ def build(verbose: bool = False, target: str = "all") -> str:
 
 
 def load_hybrid(build_if_missing: bool = False):
-    """libpie_b200_hybrid.so.  build_if_missing: compile it on first use (the servers' and the trace runner's choice;
-    a library import stays free of side effects)."""
+    """libpie_b200_hybrid.so.  build_if_missing: run `make hybrid` first -- compiles on first use and after a source
+    change, a no-op otherwise (the servers' and the trace runner's choice; a plain import stays free of side effects)."""
     global _hyb
     if _hyb is None:
+        if build_if_missing and not os.environ.get("PIE_HYBRID_LIB"):
+            try:                       # incremental: nothing happens when the library is newer than its sources
+                build(target="hybrid")
+            except (OSError, subprocess.CalledProcessError):
+                if not os.path.exists(HYBRID_LIB_PATH):
+                    raise              # a read-only checkout or a box without nvcc still runs a library that is there
         if not os.path.exists(HYBRID_LIB_PATH):
-            if not build_if_missing:
-                raise RuntimeError(f"{HYBRID_LIB_PATH} is missing: build it with `make -C {CSRC} hybrid`. "
-                                   "proxy_inference_engine_b200 has no CPU fallback.")
-            build(target="hybrid")
+            raise RuntimeError(f"{HYBRID_LIB_PATH} is missing: build it with `make -C {CSRC} hybrid`. "
+                               "proxy_inference_engine_b200 has no CPU fallback.")
         L = C.CDLL(HYBRID_LIB_PATH)
         for name, (res, args) in list(HYBRID_SIGNATURES.items()) + [(k, v) for k, v in SIGNATURES.items()
                                                                       if k.startswith("pie_page_")]:
