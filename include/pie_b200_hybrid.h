@@ -40,7 +40,8 @@ enum {
   PIEH_EPI_NONE = 0,
   PIEH_EPI_RELU2 = 1,    /* y <- max(y, 0)^2                                   */
   PIEH_EPI_SOFTCAP = 2,  /* y <- cap * tanh(y / cap)                           */
-  PIEH_EPI_STREAMS = 3   /* out is the residual [M, S, N] fp32: x[m, t, n] <- sum_s mix[s, t] x[m, s, n] + outw[t] * y */
+  PIEH_EPI_STREAMS = 3,  /* out is the residual [M, S, N] fp32: x[m, t, n] <- sum_s mix[s, t] x[m, s, n] + outw[t] * y */
+  PIEH_EPI_GLU = 4       /* gated pair (pieh_linear_glu only): out [M, N / 2]                                        */
 };
 
 /* ragged step descriptor, shared by the recurrent and the attention operators (all arrays int32, device) */
@@ -123,6 +124,93 @@ int pieh_attn_prepare(float* q_out, const float* proj, long long ld, const pieh_
                       void* stream);
 /* out[t, h, :] act [T, H dv]: both maps' windowed softmax attention over the pages, combined and normalised. */
 int pieh_attn_run(void* out, int out_dtype, const float* q, const pieh_attn* a, const pieh_batch* b, void* stream);
+
+/* ---- gated linear units -------------------------------------------------------------------------------------------
+ * w [N, K] holds the gate and the linear half INTERLEAVED: row 2 j is gate row j, row 2 j + 1 the linear ("up") row j.
+ * out[m, j] = g' * sigmoid(alpha * g') * (u' + up_offset), with g' = min(g, limit), u' = clamp(u, -limit, limit) when
+ * limit > 0 and g' = g, u' = u when limit == 0.  alpha 1, limit 0, up_offset 0 is silu(g) * u.  out is [M, N / 2]. */
+int pieh_linear_glu(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld, const void* w,
+                    int w_dtype, int M, int N, int K, float alpha, float limit, float up_offset, void* stream);
+
+/* ---- learned absolute positions and the post-norm residual ----------------------------------------------------------
+ * x[t, :] = table[tokens[t], :] + pos_table[positions[t], :] (fp32), act[t, :] = the same rounded to the act dtype
+ * (act may be NULL).  pos_table NULL: no position term. */
+int pieh_embed_positions(float* x, void* act, int act_dtype, const void* table, const void* pos_table, int table_dtype,
+                         const int32_t* tokens, const int32_t* positions, int T, int W, int vocab, int max_positions,
+                         void* stream);
+/* A sublayer's output joins the residual through its OWN norm:  x[t, :] += rms_norm(y[t, :]) * norm_w,  then
+ * act[t, :] = x[t, :] in the act dtype (the next sublayer's matrix-product input; may be NULL).
+ * y is either a plain fp32 [T, W] tensor (parts = NULL) or gathered on the fly from a mixture:
+ *   y[t, :] = sum_k part_w[t, k] * parts[part_row[t * top + k], :]  +  (shared ? shared_gate[t * gate_ld] * shared[t, :] : 0)
+ * shared_gate holds LOGITS (the sigmoid is taken here). */
+typedef struct pieh_mix_sum {
+  const float* parts;        /* [rows, W] fp32 or NULL */
+  const int32_t* part_row;   /* [T * top] */
+  const float* part_w;       /* [T * top] */
+  int top;
+  const float* shared;       /* [T, W] fp32 or NULL */
+  const float* shared_gate;  /* logits, element t * gate_ld */
+  long long gate_ld;
+} pieh_mix_sum;
+int pieh_postnorm_add(float* x, void* act, int act_dtype, const float* y, const pieh_mix_sum* mix, const float* norm_w,
+                      float eps, int T, int W, void* stream);
+
+/* ---- attention with a linear distance bias, a softmax sink and an output gate, over 64-token pages -------------------
+ * proj fp32 [T, ld]: q at column 0 (H d), k at k_off (G d), v at v_off (G dv; v_off == k_off: the values are the
+ * projected keys), gate logits at g_off (H dv; g_off < 0: no gate).
+ *   q' = rms_norm(q over all H d features) * q_norm * (1 + temp_coef * ln(floor((p + 1) / temp_every) + 1))
+ *   k' = rms_norm(k over all G d features) * k_norm            (q_norm / k_norm NULL: no norm; temp_every 0: no factor)
+ *   s_ij = q'_i . k'_j * scale - slopes[h] * (i - j),   j <= i  (and i - j < window when window > 0)
+ *   p_ij = exp(s_ij) / (sink + sum_j exp(s_ij))                 (sink 1: one extra term of score 0 without a value)
+ *   out[i, h, :] = sum_j p_ij v_j * sigmoid(gate[i, h, :]) */
+typedef struct pieh_bias_attn {
+  int H, G, d, dv;
+  long long k_off, v_off, g_off;
+  const float* q_norm;     /* [H d] */
+  const float* k_norm;     /* [G d] */
+  float eps;
+  float scale;
+  float temp_coef;
+  int temp_every;
+  const float* slopes;     /* [H] or NULL = no distance bias */
+  int sink;
+  int window;
+  void* k_pages;           /* [pages, 64, G, d]  act dtype */
+  void* v_pages;           /* [pages, 64, G, dv] act dtype */
+  int kv_dtype;
+} pieh_bias_attn;
+/* q_out fp32 [T, H, d]; k' and v appended to the pages at each row's position. */
+int pieh_bias_attn_prepare(float* q_out, const float* proj, long long ld, const pieh_bias_attn* a, const pieh_batch* b,
+                           void* stream);
+/* out act [T, H dv]; proj is read for the gate. */
+int pieh_bias_attn_run(void* out, int out_dtype, const float* q, const float* proj, long long ld,
+                       const pieh_bias_attn* a, const pieh_batch* b, void* stream);
+
+/* ---- mixture of experts ---------------------------------------------------------------------------------------------
+ * Routing of T tokens over E experts from fp32 router logits z [T, ld]:  s = sigmoid(z); the experts form n_groups equal
+ * groups of neighbours, a group scores the sum of its two largest s (its only one when a group is one expert), the
+ * keep_groups best groups stay eligible, and the `top` eligible experts with the largest s are chosen with weight
+ * s * scale (no renormalisation).  Ties go to the lower index.
+ * The plan sorts the T * top (token, choice) pairs by expert into SLOTS: slot_row[s] = token row, slot_expert[s],
+ * pair_slot[t * top + k] = slot, pair_w[t * top + k] = weight; tiles64 / tiles128 list the runs of <= 64 / 128 slots of
+ * one expert as [count, (expert, first slot, slots) ...] for the grouped products. */
+typedef struct pieh_moe_plan {
+  int E, top, n_groups, keep_groups;
+  float scale;
+  int32_t* slot_row;     /* [T * top] */
+  int32_t* slot_expert;  /* [T * top] */
+  int32_t* pair_slot;    /* [T * top] */
+  float* pair_w;         /* [T * top] */
+  int32_t* tiles64;      /* [1 + 3 * (T * top / 64 + E)]  */
+  int32_t* tiles128;     /* [1 + 3 * (T * top / 128 + E)] */
+  int32_t* counters;     /* [2 * E + 2] scratch */
+} pieh_moe_plan;
+int pieh_moe_route(const float* z, long long ld, const pieh_moe_plan* p, int T, void* stream);
+/* Grouped product over the slots: out[s, :] = x[row(s), :] W_e(s)^T with W_e = w + e * w_stride elements, row(s) =
+ * slot_row[s] when gather_rows else s.  P = T * top slots.  glu: as pieh_linear_glu (silu when alpha 1, limit 0). */
+int pieh_moe_linear(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld, const void* w,
+                    int w_dtype, long long w_stride, int P, int N, int K, int gather_rows, int glu, float alpha,
+                    float limit, float up_offset, const pieh_moe_plan* p, void* stream);
 
 #ifdef __cplusplus
 }

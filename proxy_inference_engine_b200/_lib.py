@@ -159,7 +159,30 @@ class HybAttn(C.Structure):
                 ("out_scale", C.c_float), ("k_pages", C.c_void_p), ("v_pages", C.c_void_p), ("kv_dtype", C.c_int)]
 
 
+class HybBiasAttn(C.Structure):
+    """pieh_bias_attn"""
+    _fields_ = [("H", C.c_int), ("G", C.c_int), ("d", C.c_int), ("dv", C.c_int), ("k_off", C.c_longlong),
+                ("v_off", C.c_longlong), ("g_off", C.c_longlong), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("eps", C.c_float), ("scale", C.c_float), ("temp_coef", C.c_float), ("temp_every", C.c_int),
+                ("slopes", C.c_void_p), ("sink", C.c_int), ("window", C.c_int), ("k_pages", C.c_void_p),
+                ("v_pages", C.c_void_p), ("kv_dtype", C.c_int)]
+
+
+class HybMixSum(C.Structure):
+    """pieh_mix_sum"""
+    _fields_ = [("parts", C.c_void_p), ("part_row", C.c_void_p), ("part_w", C.c_void_p), ("top", C.c_int),
+                ("shared", C.c_void_p), ("shared_gate", C.c_void_p), ("gate_ld", C.c_longlong)]
+
+
+class HybMoePlan(C.Structure):
+    """pieh_moe_plan"""
+    _fields_ = [("E", C.c_int), ("top", C.c_int), ("n_groups", C.c_int), ("keep_groups", C.c_int), ("scale", C.c_float),
+                ("slot_row", C.c_void_p), ("slot_expert", C.c_void_p), ("pair_slot", C.c_void_p), ("pair_w", C.c_void_p),
+                ("tiles64", C.c_void_p), ("tiles128", C.c_void_p), ("counters", C.c_void_p)]
+
+
 _PB, _PD, _PA = C.POINTER(HybBatch), C.POINTER(HybDelta), C.POINTER(HybAttn)
+_PBA, _PMS, _PMP = C.POINTER(HybBiasAttn), C.POINTER(HybMixSum), C.POINTER(HybMoePlan)
 # libpie_b200_hybrid.so: every symbol include/pie_b200_hybrid.h declares (tests check this), + the page allocator
 HYBRID_SIGNATURES = {
     "pieh_abi_version": (_i, []),
@@ -176,6 +199,13 @@ HYBRID_SIGNATURES = {
     "pieh_delta_gate": (_i, [_vp, _i, _vp, _vp, _ll, _ll, _PD, _i, _vp]),
     "pieh_attn_prepare": (_i, [_vp, _vp, _ll, _PA, _PB, _vp]),
     "pieh_attn_run": (_i, [_vp, _i, _vp, _PA, _PB, _vp]),
+    "pieh_linear_glu": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _i, _i, _i, _f, _f, _f, _vp]),
+    "pieh_embed_positions": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "pieh_postnorm_add": (_i, [_vp, _vp, _i, _vp, _PMS, _vp, _f, _i, _i, _vp]),
+    "pieh_bias_attn_prepare": (_i, [_vp, _vp, _ll, _PBA, _PB, _vp]),
+    "pieh_bias_attn_run": (_i, [_vp, _i, _vp, _vp, _ll, _PBA, _PB, _vp]),
+    "pieh_moe_route": (_i, [_vp, _ll, _PMP, _i, _vp]),
+    "pieh_moe_linear": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _f, _f, _f, _PMP, _vp]),
 }
 HYBRID_LIB_PATH = os.environ.get("PIE_HYBRID_LIB") or os.path.join(_HERE, "libpie_b200_hybrid.so")
 EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_STREAMS = 0, 1, 2, 3

@@ -201,7 +201,8 @@ class PagedQuantizedKVCache:
 class HybridCache:
     """What the sequences of a recurrent / attention hybrid hold between steps, for every layer at once:
 
-    * attention layers: key / value page pools ``[pages, 64, G, 2 d]`` / ``[pages, 64, G, dv]`` in the act dtype, indexed
+    * attention layers: key / value page pools ``[pages, 64, G, key_width]`` / ``[pages, 64, G, dv]`` in the act dtype
+      (key_width: 2 d for the two maps of differential attention unless the layer's spec names another), indexed
       by the page ids of ONE ``paging.PageAllocator`` (a page id names the same 64 positions in every layer's pools);
     * recurrent layers: per state slot the matrix state ``[H, dk, dv]`` and the convolution history ``[taps - 1, C]``, fp32.
 
@@ -222,7 +223,7 @@ class HybridCache:
         self.layers = []
         for spec in layer_specs:
             if spec["kind"] == "attention":
-                G, d2, dv = spec["G"], 2 * spec["d"], spec["dv"]
+                G, d2, dv = spec["G"], int(spec.get("key_width") or 2 * spec["d"]), spec["dv"]
                 self.layers.append({"k": torch.zeros((self.n_pages, self.page_size, G, d2), dtype=act_dtype, device=device),
                                     "v": torch.zeros((self.n_pages, self.page_size, G, dv), dtype=act_dtype, device=device)})
             else:

@@ -242,9 +242,14 @@ def _load_golitar(config: dict, path: str, device, dtype):
     return GolitarModel(GolitarArgs.from_dict(config), read_weights(path), device, dtype or "bfloat16")
 
 
+def _load_babodra(config: dict, path: str, device, dtype):
+    from .babodra import BabodraArgs, BabodraModel
+    return BabodraModel(BabodraArgs.from_dict(config), read_weights(path), device, dtype or "bfloat16")
+
+
 # model registry: config.json's "architecture" (or, for Hugging Face / MLX checkpoints, "model_type") -> loader.
 # The reference resolves model_type to a module of PIE/models/ the same way (PIE/models/utils.py:25-48).
-MODEL_REGISTRY = {"llama": _load_llama, "Golitar": _load_golitar}
+MODEL_REGISTRY = {"llama": _load_llama, "Golitar": _load_golitar, "Babodra": _load_babodra}
 
 
 def model_kind(config: dict) -> str:

@@ -46,7 +46,19 @@ struct LinArgs {
   int M, N, K, epi;
   float epi_a;
   const float* mix; const float* outw; int S;
+  float epi_b = 1.f, epi_c = 0.f;           // GLU: slope inside the sigmoid, offset of the linear half (epi_a: clamp, 0 = none)
+  // grouped mode (mixture of experts): the M rows are SLOTS sorted by expert
+  const int32_t* g_tiles = nullptr;         // [count, (expert, first slot, slots) ...]: blockIdx.y indexes the list
+  const int32_t* g_rows = nullptr;          // x row of each slot (NULL: the slot itself)
+  const int32_t* g_expert = nullptr;        // expert of each slot (the decode kernel: one slot per blockIdx.y)
+  long long g_wstride = 0;                  // elements between two experts' matrices
 };
+
+// the gated pair of PIEH_EPI_GLU: g the gate column, u the linear one
+__device__ __forceinline__ float glu_pair(const LinArgs& a, float g, float u) {
+  if (a.epi_a > 0.f) { g = fminf(g, a.epi_a); u = fminf(fmaxf(u, -a.epi_a), a.epi_a); }
+  return g / (1.f + expf(-a.epi_b * g)) * (u + a.epi_c);
+}
 
 template <typename T> struct elem;
 template <> struct elem<float> {

@@ -14,6 +14,7 @@ namespace pieh {
 
 cudaError_t launch_linear_umma(const LinArgs& a, int out_dtype, cudaStream_t st);   // hyb_umma.cu
 bool linear_umma_ok(const LinArgs& a, int x_dtype, int w_dtype);
+int run_linear(const LinArgs& a, int out_dtype, int x_dtype, int w_dtype, cudaStream_t st);   // picks the kernel
 
 template <typename OT>
 __device__ __forceinline__ void lin_store(const LinArgs& a, int m, int n, float y) {
@@ -34,6 +35,11 @@ __device__ __forceinline__ void lin_store(const LinArgs& a, int m, int n, float 
   elem<OT>::store(reinterpret_cast<OT*>(a.out) + (size_t)m * a.out_ld + n, y);
 }
 
+template <typename OT>
+__device__ __forceinline__ void lin_store_glu(const LinArgs& a, int m, int n_even, float g, float u) {
+  elem<OT>::store(reinterpret_cast<OT*>(a.out) + (size_t)m * a.out_ld + (n_even >> 1), glu_pair(a, g, u));
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 template <typename XT, typename WT, typename OT>
 __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
@@ -41,9 +47,17 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
   __shared__ float As[BK][BM + 4], Ws[BK][BN + 4];
   pdl_sync();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  int m0 = blockIdx.y * BM, m_end = a.M;
+  const int n0 = blockIdx.x * BN;
   const XT* x = reinterpret_cast<const XT*>(a.x);
   const WT* w = reinterpret_cast<const WT*>(a.w);
+  if (a.g_tiles) {   // grouped: this CTA's rows are one expert's run of slots
+    if ((int)blockIdx.y >= a.g_tiles[0]) return;
+    const int32_t* tl = a.g_tiles + 1 + 3 * blockIdx.y;
+    w += (size_t)tl[0] * a.g_wstride;
+    m0 = tl[1];
+    m_end = tl[1] + tl[2];
+  }
   float acc[4][4] = {};
   for (int k0 = 0; k0 < a.K; k0 += BK) {
 #pragma unroll
@@ -52,8 +66,9 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
       const int k = k0 + c;
       float xv = 0.f, wv = 0.f;
       if (k < a.K) {
-        if (m0 + r < a.M) {
-          xv = elem<XT>::load(x + (size_t)(m0 + r) * a.x_ld + k);
+        if (m0 + r < m_end) {
+          const int xr = a.g_rows ? a.g_rows[m0 + r] : m0 + r;
+          xv = elem<XT>::load(x + (size_t)xr * a.x_ld + k);
           xv = elem<WT>::round(xv);   // bf16 weights: bf16 x bf16 products, exact in fp32
         }
         if (n0 + r < a.N) wv = elem<WT>::load(w + (size_t)(n0 + r) * a.K + k);
@@ -74,12 +89,22 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
     }
     __syncthreads();
   }
+  if (a.epi == PIEH_EPI_GLU) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+        if (m < m_end && n + 1 < a.N) lin_store_glu<OT>(a, m, n, acc[i][j], acc[i][j + 1]);
+      }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-      if (m < a.M && n < a.N) lin_store<OT>(a, m, n, acc[i][j]);
+      if (m < m_end && n < a.N) lin_store<OT>(a, m, n, acc[i][j]);
     }
 }
 
@@ -110,6 +135,13 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
   const int n0 = blockIdx.x * R;
   const XT* x = reinterpret_cast<const XT*>(a.x);
   const WT* w = reinterpret_cast<const WT*>(a.w);
+  int mb = 0, M = a.M;   // grouped: one slot per blockIdx.y, with its own expert's matrix
+  if (a.g_expert) {
+    mb = blockIdx.y;
+    M = 1;
+    w += (size_t)a.g_expert[mb] * a.g_wstride;
+    x += (size_t)(a.g_rows ? a.g_rows[mb] : mb) * a.x_ld;
+  }
   float acc[MR][R];
 #pragma unroll
   for (int m = 0; m < MR; ++m)
@@ -122,7 +154,7 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
     for (int r = 0; r < R; ++r) vec8<WT>::load(w + (size_t)min(n0 + r, a.N - 1) * a.K + k, wv[r]);
 #pragma unroll
     for (int m = 0; m < MR; ++m) {
-      if (m < a.M) {
+      if (m < M) {
         float xv[8];
         vec8<XT>::load(x + (size_t)m * a.x_ld + k, xv);
 #pragma unroll
@@ -142,12 +174,23 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
       if (lane == 0) part[warp][m][r] = y;
     }
   __syncthreads();
+  if (R % 2 == 0 && a.epi == PIEH_EPI_GLU) {   // the (gate, linear) pairs of this CTA's rows
+    constexpr int RP = R > 1 ? R / 2 : 1;
+    for (int e = threadIdx.x; e < MR * RP; e += 256) {
+      const int m = e / RP, r = 2 * (e - m * RP);
+      float g = 0.f, u = 0.f;
+#pragma unroll
+      for (int wp = 0; wp < 8; ++wp) { g += part[wp][m][r]; u += part[wp][m][r + 1]; }
+      if (m < M && n0 + r + 1 < a.N) lin_store_glu<OT>(a, mb + m, n0 + r, g, u);
+    }
+    return;
+  }
   for (int e = threadIdx.x; e < MR * R; e += 256) {
     const int m = e / R, r = e - m * R;
     float y = 0.f;
 #pragma unroll
     for (int wp = 0; wp < 8; ++wp) y += part[wp][m][r];
-    if (m < a.M && n0 + r < a.N) lin_store<OT>(a, m, n0 + r, y);
+    if (m < M && n0 + r < a.N) lin_store<OT>(a, mb + m, n0 + r, y);
   }
 }
 
@@ -157,9 +200,21 @@ static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
                       (reinterpret_cast<uintptr_t>(a.w) & 31) == 0;
   count_launch();
   cudaError_t e = cudaSuccess;
-  if (a.M <= 32 && vec_ok) {
+  if (a.g_tiles) {
+    // grouped: few slots -> a CTA per (slot, output rows) streaming that slot's expert; else 64-slot tiles of one expert
+    if (a.M <= 32 && vec_ok) {
+      const bool wide = (long long)a.N * a.M >= 4 * 4 * num_sms();
+      if (wide) e = launch_k(linear_rows_kernel<XT, WT, OT, 1, 4>, dim3((a.N + 3) / 4, a.M), dim3(256), 0, st, a);
+      else e = launch_k(linear_rows_kernel<XT, WT, OT, 1, 2>, dim3((a.N + 1) / 2, a.M), dim3(256), 0, st, a);
+    } else {
+      LinArgs t = a;
+      t.g_expert = nullptr;
+      const dim3 grid((a.N + 63) / 64, a.M / 64 + (int)a.S);   // S carries the expert count here: the tile list's bound
+      e = launch_k(linear_tile_kernel<XT, WT, OT>, grid, dim3(256), 0, st, t);
+    }
+  } else if (a.M <= 32 && vec_ok) {
     // rows per CTA: enough to amortise the activation loads, few enough that every SM still gets several CTAs
-    const bool wide = a.N >= 4 * 4 * num_sms();
+    const bool wide = a.N >= 4 * 4 * num_sms() || a.epi == PIEH_EPI_GLU;   // a gated pair needs an even row count
 #define PIEH_ROWS(MR, R) e = launch_k(linear_rows_kernel<XT, WT, OT, MR, R>, dim3((a.N + R - 1) / R), dim3(256), 0, st, a)
     if (a.M <= 1) { if (wide) PIEH_ROWS(1, 2); else PIEH_ROWS(1, 1); }
     else if (a.M <= 4) { if (wide) PIEH_ROWS(4, 4); else PIEH_ROWS(4, 2); }
@@ -187,9 +242,14 @@ extern "C" int pieh_linear(void* out, int out_dtype, long long out_ld, const voi
   if (epilogue < 0 || epilogue > PIEH_EPI_STREAMS) return PIE_EUNSUPPORTED;
   if (epilogue == PIEH_EPI_STREAMS && (!mix || !outw || S < 1 || S > 8 || out_dtype != PIE_DTYPE_F32)) return PIE_EINVAL_SHAPE;
   if (epilogue == PIEH_EPI_SOFTCAP && !(epi_a > 0.f)) return PIE_EINVAL_SHAPE;
-  if (w_dtype == PIE_DTYPE_F32 && x_dtype != PIE_DTYPE_F32) return PIE_EINVAL_DTYPE;   // exact mode is fp32 end to end
   LinArgs a{out, out_ld, x, x_ld, w, bias, M, N, K, epilogue, epi_a, mix, outw, S};
   cudaStream_t st = (cudaStream_t)stream;
+  return run_linear(a, out_dtype, x_dtype, w_dtype, st);
+}
+
+namespace pieh {
+int run_linear(const LinArgs& a, int out_dtype, int x_dtype, int w_dtype, cudaStream_t st) {
+  if (w_dtype == PIE_DTYPE_F32 && x_dtype != PIE_DTYPE_F32) return PIE_EINVAL_DTYPE;   // exact mode is fp32 end to end
   if (linear_umma_ok(a, x_dtype, w_dtype)) return status_of(launch_linear_umma(a, out_dtype, st));
   typedef __nv_bfloat16 bf;
   cudaError_t e;
@@ -201,4 +261,34 @@ extern "C" int pieh_linear(void* out, int out_dtype, long long out_ld, const voi
     e = out_dtype == PIE_DTYPE_F32 ? launch_typed<bf, bf, float>(a, st) : launch_typed<bf, bf, bf>(a, st);
   }
   return status_of(e);
+}
+}  // namespace pieh
+
+extern "C" int pieh_linear_glu(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld,
+                               const void* w, int w_dtype, int M, int N, int K, float alpha, float limit, float up_offset,
+                               void* stream) {
+  if (!out || !x || !w) return PIE_ENULL;
+  if (M < 0 || N <= 0 || K <= 0 || (N & 1) || limit < 0.f) return PIE_EINVAL_SHAPE;
+  if (M == 0) return PIE_OK;
+  LinArgs a{out, out_ld, x, x_ld, w, nullptr, M, N, K, PIEH_EPI_GLU, limit, nullptr, nullptr, 0};
+  a.epi_b = alpha;
+  a.epi_c = up_offset;
+  return run_linear(a, out_dtype, x_dtype, w_dtype, (cudaStream_t)stream);
+}
+
+extern "C" int pieh_moe_linear(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld,
+                               const void* w, int w_dtype, long long w_stride, int P, int N, int K, int gather_rows, int glu,
+                               float alpha, float limit, float up_offset, const pieh_moe_plan* p, void* stream) {
+  if (!out || !x || !w || !p || !p->tiles64 || !p->tiles128 || !p->slot_row || !p->slot_expert) return PIE_ENULL;
+  if (P < 0 || N <= 0 || K <= 0 || (glu && (N & 1)) || p->E < 1 || limit < 0.f) return PIE_EINVAL_SHAPE;
+  if (P == 0) return PIE_OK;
+  LinArgs a{out, out_ld, x, x_ld, w, nullptr, P, N, K, glu ? PIEH_EPI_GLU : PIEH_EPI_NONE, glu ? limit : 0.f, nullptr, nullptr,
+            p->E};
+  a.epi_b = alpha;
+  a.epi_c = up_offset;
+  a.g_tiles = p->tiles64;
+  a.g_rows = gather_rows ? p->slot_row : nullptr;
+  a.g_expert = p->slot_expert;
+  a.g_wstride = w_stride;
+  return run_linear(a, out_dtype, x_dtype, w_dtype, (cudaStream_t)stream);
 }
