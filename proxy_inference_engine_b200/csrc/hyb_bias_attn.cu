@@ -164,6 +164,217 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
   }
 }
 
+// ---- prompt portions on the tensor cores ---------------------------------------------------------------------------
+// A CTA of 4 warps owns one 64-row query tile (consecutive positions of ONE sequence) of one query head; key tiles are
+// whole pages (64 keys) from the first page the window reaches to the page of the tile's last row, double-buffered in
+// XOR-swizzled shared memory by cp.async.  S = Q K^T on mma.sync.m16n8k16 (bf16 in, fp32 out); scale, distance bias,
+// causal and window mask, online softmax in fp32 (exp2 domain) whose running maximum starts at the sink's score 0, P
+// rounded to bf16, O += P V.  The end adds the sink to the denominator, applies the output gate and stores bf16.
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void cp16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+template <int ROWB>   // bytes of a tile row (>= 128); 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+__device__ __forceinline__ uint32_t tile_off(int r, int c) { return (uint32_t)(r * ROWB + ((c ^ (r & 7)) << 4)); }
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, const float* q, const float* proj, long long ld,
+                                                        const pieh_bias_attn a, const pieh_batch b) {
+  constexpr int KC = D / 16, NT = 8, DT = DV / 8;
+  constexpr int KROWB = D * 2, VROWB = DV * 2;
+  constexpr int KTILE = 64 * KROWB, VTILE = 64 * VROWB;
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_sync();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int tile = blockIdx.x, h = blockIdx.y;
+  const int i = b.tile_seq[tile], row0 = b.tile_row[tile];
+  const int nrows = min(64, b.seq_start[i] + b.seq_len[i] - row0);
+  const int pos0 = b.tok_pos[row0];
+  const int kvh = h / (a.H / a.G);
+  const int last_key = pos0 + nrows - 1;
+  const int first_key = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  const int j_lo = first_key / kPage, j_hi = last_key / kPage;
+  const int32_t* table = b.block_table + (size_t)i * b.bt_stride;
+  const __nv_bfloat16* kpool = reinterpret_cast<const __nv_bfloat16*>(a.k_pages);
+  const __nv_bfloat16* vpool = reinterpret_cast<const __nv_bfloat16*>(a.v_pages);
+  const uint32_t sK = (uint32_t)__cvta_generic_to_shared(smem), sV = sK + 2 * KTILE;
+
+  auto issue = [&](int j) {
+    const size_t page = (size_t)table[j] * kPage;
+    const uint32_t dk = sK + ((j - j_lo) & 1) * KTILE, dvv = sV + ((j - j_lo) & 1) * VTILE;
+    constexpr int CK = KROWB / 16, CV = VROWB / 16;
+    for (int e = tid; e < 64 * CK; e += 128) {
+      const int r = e / CK, c = e - r * CK;
+      cp16(dk + tile_off<KROWB>(r, c), kpool + ((page + r) * a.G + kvh) * D + c * 8);
+    }
+    for (int e = tid; e < 64 * CV; e += 128) {
+      const int r = e / CV, c = e - r * CV;
+      cp16(dvv + tile_off<VROWB>(r, c), vpool + ((page + r) * a.G + kvh) * DV + c * 8);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  issue(j_lo);
+
+  // Q fragments: rows 16 warp + g and + 8 of the tile (rows past the tile's end repeat its last row)
+  const int r0 = warp * 16 + g, r1 = r0 + 8;
+  uint32_t qf[KC][4];
+  {
+    const float* q0 = q + ((size_t)(row0 + min(r0, nrows - 1)) * a.H + h) * D;
+    const float* q1 = q + ((size_t)(row0 + min(r1, nrows - 1)) * a.H + h) * D;
+#pragma unroll
+    for (int kc = 0; kc < KC; ++kc) {
+      const float2 x0 = *reinterpret_cast<const float2*>(q0 + kc * 16 + 2 * t4);
+      const float2 x1 = *reinterpret_cast<const float2*>(q1 + kc * 16 + 2 * t4);
+      const float2 x2 = *reinterpret_cast<const float2*>(q0 + kc * 16 + 8 + 2 * t4);
+      const float2 x3 = *reinterpret_cast<const float2*>(q1 + kc * 16 + 8 + 2 * t4);
+      qf[kc][0] = pack2(x0.x, x0.y); qf[kc][1] = pack2(x1.x, x1.y);
+      qf[kc][2] = pack2(x2.x, x2.y); qf[kc][3] = pack2(x3.x, x3.y);
+    }
+  }
+  float o[DT][4];
+#pragma unroll
+  for (int x = 0; x < DT; ++x) o[x][0] = o[x][1] = o[x][2] = o[x][3] = 0.f;
+  const float m_init = a.sink ? 0.f : -INFINITY;
+  float mrun[2] = {m_init, m_init}, lrun[2] = {0.f, 0.f};
+  const int p0 = pos0 + min(r0, nrows - 1), p1 = pos0 + min(r1, nrows - 1);   // positions of this thread's two rows
+  const int w0 = a.window > 0 ? p0 - a.window + 1 : 0, w1 = a.window > 0 ? p1 - a.window + 1 : 0;
+  const float slope = a.slopes ? a.slopes[h] : 0.f;
+  constexpr float kLog2e = 1.4426950408889634f;
+
+  for (int j = j_lo; j <= j_hi; ++j) {
+    if (j < j_hi) { issue(j + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const uint32_t tk = sK + ((j - j_lo) & 1) * KTILE, tv = sV + ((j - j_lo) & 1) * VTILE;
+    float s[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+      for (int kc = 0; kc < KC; kc += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(tk + tile_off<KROWB>(n * 8 + (lane & 7), kc * 2 + (lane >> 3)), b0, b1, b2, b3);
+        mma_16816(s[n], qf[kc][0], qf[kc][1], qf[kc][2], qf[kc][3], b0, b1);
+        mma_16816(s[n], qf[kc + 1][0], qf[kc + 1][1], qf[kc + 1][2], qf[kc + 1][3], b2, b3);
+      }
+    }
+    const int key0 = j * kPage + 2 * t4;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const int k = key0 + n * 8;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = k + (e & 1), pr = e < 2 ? p0 : p1, wl = e < 2 ? w0 : w1;
+        const float v = s[n][e] * a.scale - slope * (float)(pr - key);
+        s[n][e] = (key <= pr && key >= wl) ? v * kLog2e : -INFINITY;
+      }
+      mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    if (mx0 > mrun[0]) {
+      const float c = exp2f(mrun[0] - mx0);   // running maximum -inf: 0, and everything it multiplies is 0
+      lrun[0] *= c;
+#pragma unroll
+      for (int x = 0; x < DT; ++x) { o[x][0] *= c; o[x][1] *= c; }
+      mrun[0] = mx0;
+    }
+    if (mx1 > mrun[1]) {
+      const float c = exp2f(mrun[1] - mx1);
+      lrun[1] *= c;
+#pragma unroll
+      for (int x = 0; x < DT; ++x) { o[x][2] *= c; o[x][3] *= c; }
+      mrun[1] = mx1;
+    }
+    const float ms0 = mrun[0] == -INFINITY ? 0.f : mrun[0], ms1 = mrun[1] == -INFINITY ? 0.f : mrun[1];
+    float ps0 = 0.f, ps1 = 0.f;
+    uint32_t pf[NT][2];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const float e0 = exp2f(s[n][0] - ms0), e1 = exp2f(s[n][1] - ms0);
+      const float e2 = exp2f(s[n][2] - ms1), e3 = exp2f(s[n][3] - ms1);
+      ps0 += e0 + e1; ps1 += e2 + e3;
+      pf[n][0] = pack2(e0, e1);
+      pf[n][1] = pack2(e2, e3);
+    }
+    lrun[0] += ps0; lrun[1] += ps1;
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const uint32_t a0 = pf[2 * kk][0], a1 = pf[2 * kk][1], a2 = pf[2 * kk + 1][0], a3 = pf[2 * kk + 1][1];
+#pragma unroll
+      for (int dj = 0; dj < DT; dj += 2) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_trans(tv + tile_off<VROWB>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dj + (lane >> 4)), b0, b1, b2, b3);
+        mma_16816(o[dj], a0, a1, a2, a3, b0, b1);
+        mma_16816(o[dj + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    __syncthreads();   // the stage is refilled two iterations from now
+  }
+  float inv[2];
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    float l = lrun[rr];
+    l += __shfl_xor_sync(0xffffffffu, l, 1); l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (a.sink) l += exp2f(-mrun[rr]);   // the sink's score 0 against the running maximum
+    inv[rr] = 1.f / l;
+  }
+  const float* g0 = a.g_off >= 0 ? proj + (size_t)(row0 + min(r0, nrows - 1)) * ld + a.g_off + (size_t)h * DV : nullptr;
+  const float* g1 = a.g_off >= 0 ? proj + (size_t)(row0 + min(r1, nrows - 1)) * ld + a.g_off + (size_t)h * DV : nullptr;
+#pragma unroll
+  for (int x = 0; x < DT; ++x) {
+    const int c = x * 8 + 2 * t4;
+    float y0 = o[x][0] * inv[0], y1 = o[x][1] * inv[0], y2 = o[x][2] * inv[1], y3 = o[x][3] * inv[1];
+    if (g0) {
+      y0 *= 1.f / (1.f + __expf(-g0[c])); y1 *= 1.f / (1.f + __expf(-g0[c + 1]));
+      y2 *= 1.f / (1.f + __expf(-g1[c])); y3 *= 1.f / (1.f + __expf(-g1[c + 1]));
+    }
+    if (r0 < nrows) *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r0) * a.H + h) * DV + c) = pack2(y0, y1);
+    if (r1 < nrows) *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r1) * a.H + h) * DV + c) = pack2(y2, y3);
+  }
+}
+
+template <int D, int DV>
+static cudaError_t launch_tile(__nv_bfloat16* out, const float* q, const float* proj, long long ld, const pieh_bias_attn& a,
+                               const pieh_batch& b, cudaStream_t st) {
+  constexpr int smem = 2 * (64 * D * 2 + 64 * DV * 2);
+  static unsigned long long configured = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!(configured >> (dev & 63) & 1)) {
+    cudaError_t e = cudaFuncSetAttribute(bias_tile_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    configured |= 1ull << (dev & 63);
+  }
+  return launch_k(bias_tile_kernel<D, DV>, dim3(b.n_tiles, a.H), dim3(128), smem, st, out, q, proj, ld, a, b);
+}
+
+// the tile kernel serves steps that are mostly prompt portions, over bf16 pages, at the head sizes it is built for
+static bool tile_ok(const pieh_bias_attn& a, const pieh_batch& b, int out_dtype) {
+  static const bool off = [] { const char* e = getenv("PIE_HYBRID_NO_TILE_ATTN"); return e && e[0] == '1'; }();
+  return !off && a.kv_dtype == PIE_DTYPE_BF16 && out_dtype == PIE_DTYPE_BF16 && a.d == a.dv && (a.d == 64 || a.d == 128) &&
+         b.n_tiles > 0 && b.tile_seq && b.tile_row && a.H <= 65535 && (long long)b.T >= 16LL * b.n_seq;
+}
+
 static bool bias_attn_ok(const pieh_bias_attn* a) {
   return a && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->d > 0 && a->dv > 0 && a->dv <= 256 && a->d <= 1024 &&
          a->k_pages && a->v_pages && a->temp_every >= 0 && a->window >= 0 && a->k_off >= 0 && a->v_off >= 0;
@@ -204,6 +415,10 @@ extern "C" int pieh_bias_attn_run(void* out, int out_dtype, const float* q, cons
   typedef __nv_bfloat16 bf;
   count_launch();
   cudaError_t e;
+  if (tile_ok(*a, *b, out_dtype)) {
+    e = a->d == 64 ? launch_tile<64, 64>((bf*)out, q, proj, ld, *a, *b, st) : launch_tile<128, 128>((bf*)out, q, proj, ld, *a, *b, st);
+    return status_of(e);
+  }
   if (a->kv_dtype == PIE_DTYPE_BF16)
     e = out_dtype == PIE_DTYPE_BF16 ? launch_run<bf, bf>((bf*)out, q, proj, ld, *a, *b, st)
                                     : launch_run<bf, float>((float*)out, q, proj, ld, *a, *b, st);

@@ -1,0 +1,270 @@
+"""Babodra on the GPU against the plain restatement of tests/babodra_oracle.py: every mechanism alone, prompts against
+token-by-token decoding, portions down to two tokens, mixed batches, re-used pages, far keys and page borders, the first
+tokens of a sequence, long decoding, sizes where head counts / groups collapse to 1, and greedy generation."""
+import copy
+import ctypes as C
+
+import pytest
+import torch
+
+import babodra_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL32, TOL16 = 2e-4, 5e-2
+
+
+def make(cfg=None, seed=0, dtype="float32", edit=None, **kw):
+    from proxy_inference_engine_b200.babodra import BabodraArgs, BabodraModel, random_weights
+    cfg = copy.deepcopy(cfg) if cfg else O.random_config(**kw)
+    args = BabodraArgs.from_dict(cfg)
+    w = random_weights(args, seed=seed)
+    for name, fn in (edit or {}).items():
+        w[name] = fn(w[name].float()).to(torch.bfloat16)
+    return cfg, w, BabodraModel(args, w, "cuda", dtype)
+
+
+def engine(model, max_tokens=1024, max_seqs=4, graph=True):
+    from proxy_inference_engine_b200.engine import HybridEngine
+    return HybridEngine(model, max_tokens, max_seqs, use_graph=graph)
+
+
+def toks(n, vocab=96, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def err(got, want):
+    got, want = got.double().cpu(), want.double()
+    return float(((got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-9)).max())
+
+
+def whole(eng, ids, sid="w"):
+    out = eng.forward([(sid, ids, list(range(len(ids))))])
+    eng.finish(sid)
+    return out
+
+
+def lib():
+    from proxy_inference_engine_b200 import _lib
+    return _lib.load_hybrid(build_if_missing=True)
+
+
+p_ = lambda t: None if t is None else C.c_void_p(t.data_ptr())
+
+
+# ---- mechanisms alone -------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kinds", [[None], ["dense"], ["moe"], ["moe", "dense", None, "moe"]],
+                         ids=["attention", "dense", "moe", "stack"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_match_the_oracle(kinds, dtype):
+    cfg, w, model = make(dtype=dtype, kinds=kinds, n_layers=len(kinds))
+    ids = toks(41)
+    trace, want_layers = [], []
+    got = engine(model).forward([("a", ids, list(range(len(ids))))], trace=trace)
+    want = O.forward(cfg, w, ids, layers_out=want_layers, rnd=O.ident if dtype == "float32" else O.bf16_round)
+    tol = TOL32 if dtype == "float32" else TOL16
+    for i, t in enumerate(trace):
+        assert err(t, want_layers[i]) < tol, f"residual after layer {i}"
+    assert err(got, want) < tol
+
+
+def test_gated_pair_epilogue_in_every_linear_kernel():
+    """pieh_linear_glu over interleaved rows: few rows, tiles, ragged edges, the tensor-core path; clamped and plain."""
+    from proxy_inference_engine_b200.babodra import interleave_pairs
+    L = lib()
+    g = torch.Generator().manual_seed(0)
+    for M, ff, K in [(1, 48, 64), (3, 25, 200), (9, 64, 72), (70, 50, 99), (200, 160, 256), (130, 96, 128)]:
+        for exact in (True, False):
+            for alpha, limit, off in ((1.702, 0.9, 1.0), (1.0, 0.0, 0.0)):
+                x = torch.randn((M, K), generator=g)
+                wg, wu = [(2 * torch.randn((ff, K), generator=g) / K ** 0.5).to(torch.bfloat16) for _ in range(2)]
+                wd = interleave_pairs(wg, wu)
+                wd = wd.float().cuda() if exact else wd.cuda()
+                xd = x.cuda() if exact else x.to(torch.bfloat16).cuda()
+                out = torch.empty((M, ff), dtype=torch.float32, device="cuda")
+                code = 1 if exact else 0
+                assert L.pieh_linear_glu(p_(out), 1, ff, p_(xd), code, K, p_(wd), code, M, 2 * ff, K, alpha, limit, off, None) == 0
+                xr = xd.double().cpu()
+                gg, uu = xr @ wg.double().T, xr @ wu.double().T
+                if limit > 0:
+                    gg, uu = gg.clamp(max=limit), uu.clamp(-limit, limit)
+                want = gg * torch.sigmoid(alpha * gg) * (uu + off)
+                assert err(out, want) < 1e-5, (M, ff, K, exact, alpha)
+
+
+@pytest.mark.parametrize("E,top,groups,keep", [(6, 2, 3, 2), (8, 4, 2, 1), (5, 1, 1, 1), (4, 4, 4, 4), (12, 3, 6, 2), (64, 6, 8, 3)])
+def test_routing_alone(E, top, groups, keep):
+    """pieh_moe_route against the restatement: choices, weights, and a plan whose slots are a permutation sorted by expert."""
+    from proxy_inference_engine_b200._lib import HybMoePlan
+    L = lib()
+    T = 77
+    g = torch.Generator().manual_seed(E)
+    z = 3 * torch.randn((T, E + 1), generator=g)
+    r = {"experts": E, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}
+    s = torch.sigmoid(z[:, :E].double())
+    idx, wt = O.route(z[:, :E].double(), torch.eye(E, dtype=torch.float64), r)     # router weight = identity: logits = z
+    P = T * top
+    i32 = lambda n: torch.zeros((n,), dtype=torch.int32, device="cuda")
+    bufs = [i32(P), i32(P), i32(P), torch.zeros((P,), device="cuda"), i32(1 + 3 * (P // 64 + E)), i32(1 + 3 * (P // 128 + E))]
+    counters = i32(2 * E + 2)
+    plan = HybMoePlan(E, top, groups, keep, 2.5, *[b.data_ptr() for b in bufs], counters.data_ptr())
+    zd = z.cuda()
+    for _ in range(2):          # twice: the counters must come back to zero
+        assert L.pieh_moe_route(p_(zd), E + 1, C.byref(plan), T, None) == 0
+    slot_row, slot_expert, pair_slot, pair_w, t64, t128 = [b.cpu() for b in bufs]
+    got_e = slot_expert[pair_slot.long()].view(T, top)
+    assert sorted(pair_slot.tolist()) == list(range(P))
+    assert torch.equal(slot_row[pair_slot.long()].view(T, top), torch.arange(T, dtype=torch.int32)[:, None].expand(T, top))
+    assert torch.equal(got_e.sort(-1).values.long(), idx.sort(-1).values)
+    assert torch.allclose(pair_w.view(T, top).double(), s.gather(1, got_e.long()) * 2.5, rtol=1e-5)
+    assert slot_expert.tolist() == sorted(slot_expert.tolist())
+    for tiles, rows in ((t64, 64), (t128, 128)):
+        covered = []
+        for k in range(int(tiles[0])):
+            e, first, n = tiles[1 + 3 * k: 4 + 3 * k].tolist()
+            assert 0 < n <= rows and set(slot_expert[first: first + n].tolist()) == {e}
+            covered += list(range(first, first + n))
+        assert covered == list(range(P))
+    assert int(counters.abs().sum()) == 0
+
+
+def test_distance_bias_and_sink_show_in_one_head():
+    """One query is made to match one far key strongly: the output then depends on the exact distance term and on the
+    sink's share, which random weights would drown among hundreds of keys."""
+    cfg, w, model = make(kinds=[None], n_layers=1, heads=4, kv_heads=4, dim=16, width=64, scale=2.0,
+                         edit={"l0.mix.q": lambda t: t * 4, "l0.mix.k": lambda t: t * 4})
+    ids = toks(300)
+    assert err(whole(engine(model), ids), O.forward(cfg, w, ids)) < TOL32
+
+
+# ---- schedules --------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefill_against_token_by_token_decoding(dtype):
+    cfg, w, model = make(dtype=dtype)
+    ids = toks(150)
+    want = O.forward(cfg, w, ids, rnd=O.ident if dtype == "float32" else O.bf16_round)
+    eng = engine(model)
+    got = [eng.forward([("s", ids[:70], list(range(70)))])]
+    for t in range(70, 150):                   # crosses the page borders at 128 and the temperature steps at 24 k - 1
+        got.append(eng.forward([("s", [ids[t]], [0])]))
+    assert err(torch.cat(got), want) < (TOL32 if dtype == "float32" else TOL16)
+
+
+@pytest.mark.parametrize("sizes", [[2, 2, 3, 61, 2, 64, 1, 1, 65], [63, 1, 1, 63, 2, 69], [1] * 5 + [194]])
+def test_portions_of_several_sizes(sizes):
+    cfg, w, model = make()
+    ids = toks(sum(sizes))
+    eng, got, at = engine(model), [], 0
+    for n in sizes:
+        got.append(eng.forward([("s", ids[at: at + n], list(range(n)))]))
+        at += n
+    assert err(torch.cat(got), O.forward(cfg, w, ids)) < TOL32
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_batches_match_each_request_alone(dtype):
+    """Four requests of unequal length advance together -- portions beside single tokens -- through a pool too small for
+    all of them at once, so pages and slots are handed on; each must match the same request run alone."""
+    cfg, w, model = make(dtype=dtype)
+    rnd = O.ident if dtype == "float32" else O.bf16_round
+    reqs = {n: toks(m, seed=10 + i) for i, (n, m) in enumerate((("a", 200), ("b", 90), ("c", 33), ("d", 130), ("e", 70)))}
+    want = {n: O.forward(cfg, w, ids, rnd=rnd) for n, ids in reqs.items()}
+    eng = engine(model, max_tokens=576, max_seqs=4)
+    plan = [[("a", 64), ("b", 2)], [("a", 1), ("b", 50), ("c", 33)], [("a", 100), ("b", 1), ("d", 3)],
+            [("a", 35), ("b", 37), ("d", 61)], [("d", 2), ("e", 30)], [("d", 64), ("e", 1)], [("e", 39)]]
+    at, got = {n: 0 for n in reqs}, {n: [] for n in reqs}
+    for step in plan:
+        entries = []
+        for n, m in step:
+            entries.append((n, reqs[n][at[n]: at[n] + m], list(range(m))))
+            at[n] += m
+        out = eng.forward(entries)
+        o = 0
+        for n, m in step:
+            got[n].append(out[o: o + m])
+            o += m
+        for n, _ in step:
+            if at[n] == len(reqs[n]):
+                eng.finish(n)
+    tol = TOL32 if dtype == "float32" else TOL16
+    for n in reqs:
+        assert at[n] == len(reqs[n])
+        assert err(torch.cat(got[n]), want[n]) < tol, n
+
+
+def test_pages_and_slots_are_used_again():
+    cfg, w, model = make(kinds=["moe", "dense"], n_layers=2)
+    eng = engine(model, max_tokens=192, max_seqs=1)
+    for k in range(4):
+        ids = toks(100 + 20 * k, seed=k)
+        got = whole(eng, ids, sid=f"r{k}")
+        assert err(got, O.forward(cfg, w, ids)) < TOL32
+    assert eng.cache.allocator.get_num_free_pages() == eng.cache.n_pages
+
+
+def test_first_tokens_and_single_token_sequences():
+    cfg, w, model = make()
+    eng = engine(model)
+    for n in (1, 2, 3):
+        ids = toks(n, seed=n)
+        assert err(whole(eng, ids), O.forward(cfg, w, ids)) < TOL32
+    a, b = toks(1, seed=7), toks(1, seed=8)
+    out = eng.forward([("a", a, [0]), ("b", b, [0])])
+    assert err(out[:1], O.forward(cfg, w, a)) < TOL32 and err(out[1:], O.forward(cfg, w, b)) < TOL32
+
+
+def test_long_decoding_through_captured_steps():
+    """300 single-token steps of two sequences side by side (the captured decode graph), bf16, against the restatement."""
+    cfg, w, model = make(dtype="bfloat16", kinds=["moe", "dense"], n_layers=2)
+    a, b = toks(330, seed=3), toks(310, seed=4)
+    eng = engine(model, graph=True)
+    eng.forward([("a", a[:30], []), ("b", b[:10], [])])
+    ga, gb = [], []
+    for t in range(300):
+        out = eng.forward([("a", [a[30 + t]], [0]), ("b", [b[10 + t]], [0])])
+        ga.append(out[:1].clone())
+        gb.append(out[1:].clone())
+    assert err(torch.cat(ga), O.forward(cfg, w, a, rnd=O.bf16_round)[30:]) < TOL16
+    assert err(torch.cat(gb), O.forward(cfg, w, b, rnd=O.bf16_round)[10:]) < TOL16
+
+
+@pytest.mark.parametrize("kw", [dict(heads=1, kv_heads=1, dim=8, width=24), dict(heads=6, kv_heads=1, dim=24),
+                                dict(heads=3, kv_heads=3, dim=40, width=56, ff=33, expert_ff=17, shared_ff=9),
+                                dict(experts=4, top=4, groups=(1, 1), shared_ff=0), dict(experts=7, top=1, groups=(7, 1)),
+                                dict(q_temp=None), dict(q_temp=(1.3, 1)), dict(heads=2, kv_heads=1, dim=64, width=128)],
+                         ids=["one-head", "one-kv-head", "odd-sizes", "all-experts", "top-1", "no-temperature",
+                              "temperature-every-1", "tile-head-size"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_sizes(kw, dtype):
+    cfg, w, model = make(dtype=dtype, **kw)
+    ids = toks(83)
+    want = O.forward(cfg, w, ids, rnd=O.ident if dtype == "float32" else O.bf16_round)
+    assert err(whole(engine(model), ids), want) < (TOL32 if dtype == "float32" else TOL16)
+
+
+def test_tile_attention_against_the_row_kernel(monkeypatch):
+    """bf16 prompt portions at a head size the tensor-core tiles serve: far keys, page borders, a portion that starts
+    in the middle of a page."""
+    cfg, w, model = make(dtype="bfloat16", heads=4, kv_heads=2, dim=64, width=128, kinds=[None, "dense"], n_layers=2)
+    ids = toks(333)
+    want = O.forward(cfg, w, ids, rnd=O.bf16_round)
+    eng = engine(model)
+    got = [eng.forward([("s", ids[:37], list(range(37)))]), eng.forward([("s", ids[37:229], list(range(192)))]),
+           eng.forward([("s", ids[229:], list(range(104)))])]
+    assert err(torch.cat(got), want) < TOL16
+
+
+def test_greedy_generation_through_the_engine():
+    cfg, w, model = make(dtype="float32")
+    prompts = [toks(40, seed=1), toks(7, seed=2), toks(90, seed=3)]
+    eng = engine(model, max_tokens=512, max_seqs=2)
+    outs = eng.generate(prompts, max_new_tokens=12, step_tokens=48)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o:                           # every generated token is the oracle's argmax given what came before
+            lg = O.forward(cfg, w, seq)[-1]
+            top2 = lg.topk(2).values
+            if float(top2[0] - top2[1]) > 1e-3:
+                assert int(lg.argmax()) == tok
+            seq.append(tok)
