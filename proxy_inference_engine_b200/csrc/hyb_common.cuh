@@ -49,6 +49,7 @@ struct LinArgs {
   float epi_b = 1.f, epi_c = 0.f;           // GLU: slope inside the sigmoid, offset of the linear half (epi_a: clamp, 0 = none)
   // grouped mode (mixture of experts): the M rows are SLOTS sorted by expert
   const int32_t* g_tiles = nullptr;         // [count, (expert, first slot, slots) ...]: blockIdx.y indexes the list
+  const int32_t* g_tiles128 = nullptr;      // the same runs cut into <= 128 slots (host side: which list a kernel gets)
   const int32_t* g_rows = nullptr;          // x row of each slot (NULL: the slot itself)
   const int32_t* g_expert = nullptr;        // expert of each slot (the decode kernel: one slot per blockIdx.y)
   long long g_wstride = 0;                  // elements between two experts' matrices

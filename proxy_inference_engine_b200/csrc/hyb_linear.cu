@@ -250,7 +250,14 @@ extern "C" int pieh_linear(void* out, int out_dtype, long long out_ld, const voi
 namespace pieh {
 int run_linear(const LinArgs& a, int out_dtype, int x_dtype, int w_dtype, cudaStream_t st) {
   if (w_dtype == PIE_DTYPE_F32 && x_dtype != PIE_DTYPE_F32) return PIE_EINVAL_DTYPE;   // exact mode is fp32 end to end
-  if (linear_umma_ok(a, x_dtype, w_dtype)) return status_of(launch_linear_umma(a, out_dtype, st));
+  // grouped products go to the tensor cores once an expert's run averages a few rows of a 128-slot tile
+  if (linear_umma_ok(a, x_dtype, w_dtype) && (!a.g_tiles || a.M >= 8 * a.S)) {
+    if (!a.g_tiles) return status_of(launch_linear_umma(a, out_dtype, st));
+    LinArgs t = a;          // the tensor-core tiles are 128 slots tall
+    t.g_tiles = a.g_tiles128;
+    t.g_expert = nullptr;
+    return status_of(launch_linear_umma(t, out_dtype, st));
+  }
   typedef __nv_bfloat16 bf;
   cudaError_t e;
   if (w_dtype == PIE_DTYPE_F32) {
@@ -287,6 +294,7 @@ extern "C" int pieh_moe_linear(void* out, int out_dtype, long long out_ld, const
   a.epi_b = alpha;
   a.epi_c = up_offset;
   a.g_tiles = p->tiles64;
+  a.g_tiles128 = p->tiles128;
   a.g_rows = gather_rows ? p->slot_row : nullptr;
   a.g_expert = p->slot_expert;
   a.g_wstride = w_stride;

@@ -76,6 +76,29 @@ __device__ __forceinline__ void umma_store(const LinArgs& a, int m, int n0, cons
     }
     return;
   }
+  if (a.epi == PIEH_EPI_GLU) {   // columns (2 j, 2 j + 1) are a (gate, linear) pair -> output column j
+    OT* dst = reinterpret_cast<OT*>(a.out) + (size_t)m * a.out_ld + (n0 >> 1);
+    float y[16];
+#pragma unroll
+    for (int q = 0; q < 16; ++q) y[q] = glu_pair(a, __uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
+    if (n0 + 32 <= a.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      if (sizeof(OT) == 4) {
+        float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) d4[q] = make_float4(y[4 * q], y[4 * q + 1], y[4 * q + 2], y[4 * q + 3]);
+      } else {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+          d4[q] = make_uint4(pie::pack_bf16(y[8 * q], y[8 * q + 1]), pie::pack_bf16(y[8 * q + 2], y[8 * q + 3]),
+                             pie::pack_bf16(y[8 * q + 4], y[8 * q + 5]), pie::pack_bf16(y[8 * q + 6], y[8 * q + 7]));
+      }
+      return;
+    }
+    for (int q = 0; q < 16; ++q)
+      if (n0 + 2 * q + 1 < a.N) elem<OT>::store(dst + q, y[q]);
+    return;
+  }
   OT* dst = reinterpret_cast<OT*>(a.out) + (size_t)m * a.out_ld;
   float y[32];
 #pragma unroll
@@ -122,7 +145,16 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smA = base, smB = base + S * A_STAGE;
-  const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * kBN;
+  int m0 = blockIdx.y * BM, m_end = a.M;
+  const __nv_bfloat16* wmat = reinterpret_cast<const __nv_bfloat16*>(a.w);
+  if (a.g_tiles) {   // grouped: this CTA's rows are one expert's run of slots (the whole CTA leaves before anything is set up)
+    if ((int)blockIdx.y >= a.g_tiles[0]) return;
+    const int32_t* tl = a.g_tiles + 1 + 3 * blockIdx.y;
+    wmat += (size_t)tl[0] * a.g_wstride;
+    m0 = tl[1];
+    m_end = tl[1] + tl[2];
+  }
   const int nk = a.K / kBK;
 
   if (tid == 0) {
@@ -144,8 +176,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
   if (warp < kProducers / 32) {
     const int t = tid;
     const uint32_t swz = (uint32_t)(t & 7);
-    const __nv_bfloat16* wsrc = reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)min(n0 + t, a.N - 1) * a.K;
-    const __nv_bfloat16* xsrc = reinterpret_cast<const __nv_bfloat16*>(a.x) + (size_t)min(m0 + min(t, BM - 1), a.M - 1) * a.x_ld;
+    const __nv_bfloat16* wsrc = wmat + (size_t)min(n0 + t, a.N - 1) * a.K;
+    const int xslot = min(m0 + min(t, BM - 1), m_end - 1);
+    const __nv_bfloat16* xsrc = reinterpret_cast<const __nv_bfloat16*>(a.x) + (size_t)(a.g_rows ? a.g_rows[xslot] : xslot) * a.x_ld;
     bool alive = true;
     for (int kb = 0; kb < nk + LAG && alive; ++kb) {
       if (kb < nk) {
@@ -182,7 +215,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
       for (int c = c_lo; c < c_hi; ++c) {
         uint32_t v[32];
         pie::tmem_ld32(tmem + (uint32_t)(h * kBN + c * 32) + ((uint32_t)(quad * 32) << 16), v);
-        if (row < a.M && n0 + c * 32 < a.N) umma_store<OT>(a, row, n0 + c * 32, v);
+        if (row < m_end && n0 + c * 32 < a.N) umma_store<OT>(a, row, n0 + c * 32, v);
       }
     }
   } else {
@@ -214,7 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
 
 bool linear_umma_ok(const LinArgs& a, int x_dtype, int w_dtype) {
   static const bool off = [] { const char* e = getenv("PIE_HYBRID_NO_UMMA"); return e && e[0] == '1'; }();
-  if (off || a.g_tiles || a.epi == PIEH_EPI_GLU) return false;
+  if (off) return false;
   return x_dtype == PIE_DTYPE_BF16 && w_dtype == PIE_DTYPE_BF16 && a.M > 32 && a.K % kBK == 0 && a.x_ld % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
 }
@@ -230,7 +263,8 @@ static cudaError_t launch_bm(const LinArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     configured |= 1ull << (dev & 63);
   }
-  const dim3 grid((a.N + kBN - 1) / kBN, (a.M + BM - 1) / BM);
+  // grouped: blockIdx.y walks the list of <= 128-slot tiles, whose length is only known on the device (S = experts)
+  const dim3 grid((a.N + kBN - 1) / kBN, a.g_tiles ? a.M / 128 + a.S : (a.M + BM - 1) / BM);
   count_launch();
   linear_umma_kernel<BM, S, OT><<<grid, kThreads, smem, st>>>(a);
   return cudaGetLastError();
@@ -243,6 +277,7 @@ cudaError_t launch_linear_umma(const LinArgs& a, int out_dtype, cudaStream_t st)
   static const int force = [] { const char* e = getenv("PIE_HYBRID_UMMA_TILE"); return e ? atoi(e) : 0; }();   // tuning
   int variant = a.M > 128 && 2 * tiles256 >= num_sms() ? 256 : 128;
   if (force == 128 || force == 256) variant = force;
+  if (a.g_tiles) variant = 128;
 #define PIEH_UMMA(OT) (variant == 256 ? launch_bm<256, 3, OT>(a, st) : launch_bm<128, 4, OT>(a, st))
   if (out_dtype == PIE_DTYPE_BF16) return PIEH_UMMA(__nv_bfloat16);
   return PIEH_UMMA(float);

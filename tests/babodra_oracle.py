@@ -84,8 +84,10 @@ def silu_expert(x, w, p, rnd=ident):
     return lin(g * torch.sigmoid(g) * lin(x, w[p + "up"], None, rnd), w[p + "down"], None, rnd)
 
 
-def route(x, w_router, r, rnd=ident):
-    """-> (chosen expert ids [T, top], their weights [T, top])."""
+def route(x, w_router, r, rnd=ident, margins=None):
+    """-> (chosen expert ids [T, top], their weights [T, top]).  margins: if a list, gets per token the smallest gap by
+    which a choice was made (last kept group against the next one, last chosen expert against the next eligible one):
+    a token with a tiny margin may legitimately be routed otherwise by an implementation that rounds differently."""
     E, top = r["experts"], r["top"]
     s = torch.sigmoid(lin(x, w_router, None, rnd))
     grp = r.get("groups") or {"count": 1, "keep": 1}
@@ -97,11 +99,20 @@ def route(x, w_router, r, rnd=ident):
     allowed = torch.zeros((x.shape[0], n), dtype=torch.bool).scatter_(1, kept, True)
     masked = torch.where(allowed[:, :, None].expand(-1, -1, per).reshape(-1, E), s, torch.full_like(s, -1.0))
     idx = masked.topk(top, -1).indices
+    if margins is not None:
+        m = torch.full((x.shape[0],), float("inf"), dtype=s.dtype)
+        if keep < n:
+            gv = gscore.sort(-1, descending=True).values
+            m = torch.minimum(m, gv[:, keep - 1] - gv[:, keep])
+        if top < keep * per:
+            ev = masked.sort(-1, descending=True).values
+            m = torch.minimum(m, ev[:, top - 1] - ev[:, top])
+        margins.append(m)
     return idx, s.gather(1, idx) * r["scale"]
 
 
-def moe_ff(x, w, p, cfg, rnd=ident):
-    idx, wt = route(x, w[p + "router"], cfg["router"], rnd)
+def moe_ff(x, w, p, cfg, rnd=ident, margins=None):
+    idx, wt = route(x, w[p + "router"], cfg["router"], rnd, margins)
     y = torch.zeros_like(x)
     for t in range(x.shape[0]):
         for e, a in zip(idx[t].tolist(), wt[t]):
@@ -111,8 +122,9 @@ def moe_ff(x, w, p, cfg, rnd=ident):
     return y
 
 
-def forward(config, weights, tokens, dtype=torch.float64, rnd=ident, layers_out=None):
-    """Logits [T, vocab] of one sequence fed whole from position 0."""
+def forward(config, weights, tokens, dtype=torch.float64, rnd=ident, layers_out=None, margins=None):
+    """Logits [T, vocab] of one sequence fed whole from position 0.  margins: if a list, one tensor [T] per mixture
+    layer is appended (see route)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = config["norm"]["eps"]
     T = len(tokens)
@@ -122,7 +134,7 @@ def forward(config, weights, tokens, dtype=torch.float64, rnd=ident, layers_out=
         x = x + rms(attention_mixer(x, w, p + "mix.", ly["mixer"], eps, rnd), eps) * w[p + "norm1"]
         mlp = ly.get("mlp")
         if mlp:
-            f = dense_ff(x, w, p + "mlp.", mlp, rnd) if mlp["kind"] == "dense" else moe_ff(x, w, p + "mlp.", mlp, rnd)
+            f = dense_ff(x, w, p + "mlp.", mlp, rnd) if mlp["kind"] == "dense" else moe_ff(x, w, p + "mlp.", mlp, rnd, margins)
             x = x + rms(f, eps) * w[p + "norm2"]
         if layers_out is not None:
             layers_out.append(x.clone())

@@ -39,6 +39,26 @@ def err(got, want):
     return float(((got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-9)).max())
 
 
+def rows_err(got, want):
+    got, want = got.double().cpu(), want.double()
+    return (got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt().clamp_min(1e-9)
+
+
+def ok16(got, want, margins):
+    """bf16 against the restatement when the model routes: a token whose routing margin is within rounding may take
+    another expert than the restatement did (and nudges the tokens that attend to it), so rows with a tiny margin are
+    left out, nine rows in ten must be within TOL16 and no other row may be off by more than four times that."""
+    e = rows_err(got, want)
+    keep = torch.stack(margins).min(0).values > 0.02 if margins else torch.ones_like(e, dtype=torch.bool)
+    e = e[keep[-len(e):]]
+    return float(e.quantile(0.9)) < TOL16 and float(e.max()) < 4 * TOL16
+
+
+def oracle16(cfg, w, ids):
+    mg = []
+    return O.forward(cfg, w, ids, rnd=O.bf16_round, margins=mg), mg
+
+
 def whole(eng, ids, sid="w"):
     out = eng.forward([(sid, ids, list(range(len(ids))))])
     eng.finish(sid)
@@ -62,11 +82,16 @@ def test_layers_match_the_oracle(kinds, dtype):
     ids = toks(41)
     trace, want_layers = [], []
     got = engine(model).forward([("a", ids, list(range(len(ids))))], trace=trace)
-    want = O.forward(cfg, w, ids, layers_out=want_layers, rnd=O.ident if dtype == "float32" else O.bf16_round)
-    tol = TOL32 if dtype == "float32" else TOL16
-    for i, t in enumerate(trace):
-        assert err(t, want_layers[i]) < tol, f"residual after layer {i}"
-    assert err(got, want) < tol
+    mg = []
+    want = O.forward(cfg, w, ids, layers_out=want_layers, rnd=O.ident if dtype == "float32" else O.bf16_round, margins=mg)
+    if dtype == "float32":
+        for i, t in enumerate(trace):
+            assert err(t, want_layers[i]) < TOL32, f"residual after layer {i}"
+        assert err(got, want) < TOL32
+    else:
+        for i, t in enumerate(trace):
+            assert ok16(t, want_layers[i], mg), f"residual after layer {i}"
+        assert ok16(got, want, mg)
 
 
 def test_gated_pair_epilogue_in_every_linear_kernel():
@@ -129,6 +154,48 @@ def test_routing_alone(E, top, groups, keep):
     assert int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("T,E,top,K,ff", [(5, 4, 2, 64, 24), (16, 8, 2, 200, 33), (70, 6, 2, 72, 40), (300, 4, 2, 128, 96),
+                                          (513, 16, 4, 64, 64)], ids=["few-slots", "few-slots-odd", "tiles", "tensor-core", "many-experts"])
+@pytest.mark.parametrize("exact", [True, False], ids=["float32", "bfloat16"])
+def test_grouped_products_alone(T, E, top, K, ff, exact):
+    """pieh_moe_linear over a routed plan: the gathered gate / up product with the silu pair, then the down product per
+    slot, against a loop over tokens and their experts."""
+    from proxy_inference_engine_b200._lib import HybMoePlan
+    from proxy_inference_engine_b200.babodra import interleave_pairs
+    L = lib()
+    g = torch.Generator().manual_seed(T)
+    z = 2 * torch.randn((T, E), generator=g)
+    x = torch.randn((T, K), generator=g)
+    wg, wu = [(2 * torch.randn((E, ff, K), generator=g) / K ** 0.5).to(torch.bfloat16) for _ in range(2)]
+    wdn = (torch.randn((E, K, ff), generator=g) / ff ** 0.5).to(torch.bfloat16)
+    P = T * top
+    i32 = lambda n: torch.zeros((n,), dtype=torch.int32, device="cuda")
+    bufs = [i32(P), i32(P), i32(P), torch.zeros((P,), device="cuda"), i32(1 + 3 * (P // 64 + E)), i32(1 + 3 * (P // 128 + E))]
+    counters = i32(2 * E + 2)
+    plan = HybMoePlan(E, top, 1, 1, 1.0, *[b.data_ptr() for b in bufs], counters.data_ptr())
+    zd = z.cuda()
+    assert L.pieh_moe_route(p_(zd), E, C.byref(plan), T, None) == 0
+    code, dt = (1, torch.float32) if exact else (0, torch.bfloat16)
+    xd = x.to(dt).cuda()
+    gu = torch.stack([interleave_pairs(wg[e], wu[e]) for e in range(E)]).to(dt).cuda().contiguous()
+    dn = wdn.to(dt).cuda().contiguous()
+    hid = torch.empty((P, ff), dtype=dt, device="cuda")
+    assert L.pieh_moe_linear(p_(hid), code, ff, p_(xd), code, K, p_(gu), code, 2 * ff * K, P, 2 * ff, K, 1, 1, 1.0, 0.0, 0.0,
+                             C.byref(plan), None) == 0
+    ys = torch.empty((P, K), dtype=torch.float32, device="cuda")
+    assert L.pieh_moe_linear(p_(ys), 1, K, p_(hid), code, ff, p_(dn), code, K * ff, P, K, ff, 0, 0, 1.0, 0.0, 0.0,
+                             C.byref(plan), None) == 0
+    torch.cuda.synchronize()
+    assert L.pieh_pipeline_error() == 0
+    slot_row, slot_expert = bufs[0].cpu().long(), bufs[1].cpu().long()
+    xr = xd.double().cpu()
+    want_h = torch.stack([O.lin(xr[slot_row[s]], wg[slot_expert[s]].double()) for s in range(P)])
+    want_h = want_h * torch.sigmoid(want_h) * torch.stack([O.lin(xr[slot_row[s]], wu[slot_expert[s]].double()) for s in range(P)])
+    assert err(hid, want_h) < (1e-5 if exact else 1e-2)
+    want_y = torch.stack([O.lin(hid[s].double().cpu(), wdn[slot_expert[s]].double()) for s in range(P)])
+    assert err(ys, want_y) < 1e-5
+
+
 def test_distance_bias_and_sink_show_in_one_head():
     """One query is made to match one far key strongly: the output then depends on the exact distance term and on the
     sink's share, which random weights would drown among hundreds of keys."""
@@ -143,12 +210,14 @@ def test_distance_bias_and_sink_show_in_one_head():
 def test_prefill_against_token_by_token_decoding(dtype):
     cfg, w, model = make(dtype=dtype)
     ids = toks(150)
-    want = O.forward(cfg, w, ids, rnd=O.ident if dtype == "float32" else O.bf16_round)
     eng = engine(model)
     got = [eng.forward([("s", ids[:70], list(range(70)))])]
     for t in range(70, 150):                   # crosses the page borders at 128 and the temperature steps at 24 k - 1
-        got.append(eng.forward([("s", [ids[t]], [0])]))
-    assert err(torch.cat(got), want) < (TOL32 if dtype == "float32" else TOL16)
+        got.append(eng.forward([("s", [ids[t]], [0])]).clone())
+    if dtype == "float32":
+        assert err(torch.cat(got), O.forward(cfg, w, ids)) < TOL32
+    else:
+        assert ok16(torch.cat(got), *oracle16(cfg, w, ids))
 
 
 @pytest.mark.parametrize("sizes", [[2, 2, 3, 61, 2, 64, 1, 1, 65], [63, 1, 1, 63, 2, 69], [1] * 5 + [194]])
@@ -167,9 +236,8 @@ def test_mixed_batches_match_each_request_alone(dtype):
     """Four requests of unequal length advance together -- portions beside single tokens -- through a pool too small for
     all of them at once, so pages and slots are handed on; each must match the same request run alone."""
     cfg, w, model = make(dtype=dtype)
-    rnd = O.ident if dtype == "float32" else O.bf16_round
     reqs = {n: toks(m, seed=10 + i) for i, (n, m) in enumerate((("a", 200), ("b", 90), ("c", 33), ("d", 130), ("e", 70)))}
-    want = {n: O.forward(cfg, w, ids, rnd=rnd) for n, ids in reqs.items()}
+    want = {n: (O.forward(cfg, w, ids), None) if dtype == "float32" else oracle16(cfg, w, ids) for n, ids in reqs.items()}
     eng = engine(model, max_tokens=576, max_seqs=4)
     plan = [[("a", 64), ("b", 2)], [("a", 1), ("b", 50), ("c", 33)], [("a", 100), ("b", 1), ("d", 3)],
             [("a", 35), ("b", 37), ("d", 61)], [("d", 2), ("e", 30)], [("d", 64), ("e", 1)], [("e", 39)]]
@@ -187,10 +255,12 @@ def test_mixed_batches_match_each_request_alone(dtype):
         for n, _ in step:
             if at[n] == len(reqs[n]):
                 eng.finish(n)
-    tol = TOL32 if dtype == "float32" else TOL16
     for n in reqs:
         assert at[n] == len(reqs[n])
-        assert err(torch.cat(got[n]), want[n]) < tol, n
+        if dtype == "float32":
+            assert err(torch.cat(got[n]), want[n][0]) < TOL32, n
+        else:
+            assert ok16(torch.cat(got[n]), *want[n]), n
 
 
 def test_pages_and_slots_are_used_again():
@@ -225,8 +295,9 @@ def test_long_decoding_through_captured_steps():
         out = eng.forward([("a", [a[30 + t]], [0]), ("b", [b[10 + t]], [0])])
         ga.append(out[:1].clone())
         gb.append(out[1:].clone())
-    assert err(torch.cat(ga), O.forward(cfg, w, a, rnd=O.bf16_round)[30:]) < TOL16
-    assert err(torch.cat(gb), O.forward(cfg, w, b, rnd=O.bf16_round)[10:]) < TOL16
+    wa, ma = oracle16(cfg, w, a)
+    wb, mb = oracle16(cfg, w, b)
+    assert ok16(torch.cat(ga), wa[30:], ma) and ok16(torch.cat(gb), wb[10:], mb)
 
 
 @pytest.mark.parametrize("kw", [dict(heads=1, kv_heads=1, dim=8, width=24), dict(heads=6, kv_heads=1, dim=24),
@@ -239,8 +310,10 @@ def test_long_decoding_through_captured_steps():
 def test_other_sizes(kw, dtype):
     cfg, w, model = make(dtype=dtype, **kw)
     ids = toks(83)
-    want = O.forward(cfg, w, ids, rnd=O.ident if dtype == "float32" else O.bf16_round)
-    assert err(whole(engine(model), ids), want) < (TOL32 if dtype == "float32" else TOL16)
+    if dtype == "float32":
+        assert err(whole(engine(model), ids), O.forward(cfg, w, ids)) < TOL32
+    else:
+        assert ok16(whole(engine(model), ids), *oracle16(cfg, w, ids))
 
 
 def test_tile_attention_against_the_row_kernel(monkeypatch):
