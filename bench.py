@@ -38,10 +38,11 @@ def parse():
     ap.add_argument("--no-70b", action="store_true", help="N > 1: skip the Llama-3.1-70B tensor-parallel sub-records")
     ap.add_argument("--no-config3", action="store_true", help="skip the 8-bit / batch-32 / paged-KV sub-record (BASELINE configs[2])")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM figure (BASELINE config 4 shapes)")
-    ap.add_argument("--family", default="llama", choices=("llama", "golitar"),
+    ap.add_argument("--family", default="llama", choices=("llama", "golitar", "babodra"),
                     help="golitar: prefill / decode throughput and per-operator rooflines of the Golitar family at --size, "
-                         "beside the quantized Llama path at equal size (its own JSON line; the default workload is untouched)")
-    ap.add_argument("--size", default="1b", help="--family golitar: layer sizes, 1b or 8b")
+                         "beside the quantized Llama path at equal size; babodra: the same for the Babodra family, beside "
+                         "Golitar at equal size (its own JSON line; the default workload is untouched)")
+    ap.add_argument("--size", default="1b", help="--family golitar | babodra: layer sizes, 1b or 8b")
     return ap.parse_args()
 
 
@@ -666,18 +667,19 @@ def run_reference(a):
 def run_golitar(a):
     from proxy_inference_engine_b200 import hybrid_bench
     rec = hybrid_bench.run(a.size, prompt=max(a.prompt, 4096) if a.prompt == 128 else a.prompt, batch=max(a.batch, 4)
-                           if a.batch == 1 else a.batch, steps=min(a.steps, 64), warmup=max(a.warmup, 3), root=ROOT)
-    line = {"metric": "golitar decode tok/s", "value": rec["decode"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
+                           if a.batch == 1 else a.batch, steps=min(a.steps, 64), warmup=max(a.warmup, 3), root=ROOT,
+                           family=a.family)
+    line = {"metric": f"{a.family} decode tok/s", "value": rec["decode"]["tok_s"], "unit": "tok/s", "n_gpus": 1,
             "steps": min(a.steps, 64), "warmup": max(a.warmup, 3), "ms_per_step": rec["decode"]["ms_per_step"],
             "higher_is_better": True, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "gpu_launches": rec["decode"]["launches_per_step"] * min(a.steps, 64), "config": {"model": f"golitar-{a.size}"}}
+            "gpu_launches": rec["decode"]["launches_per_step"] * min(a.steps, 64), "config": {"model": f"{a.family}-{a.size}"}}
     line.update(rec)
     print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
     args = parse()
-    if args.family == "golitar":
+    if args.family in ("golitar", "babodra"):
         run_golitar(args)
     elif args.impl == "reference":
         run_reference(args)

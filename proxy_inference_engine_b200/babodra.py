@@ -120,7 +120,7 @@ class BabodraModel:
             p, m = f"l{i}.", cfg["mixer"]
             H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
             mw = lambda n: get(p + "mix." + n)
-            bias = torch.cat([mw("q.b").float(), mw("k.b").float(), torch.zeros(H * dv)])
+            bias = torch.cat([mw("q.b").float(), mw("k.b").float(), torch.zeros(H * dv, device=mw("q.b").device)])
             qt = m.get("q_temp") or {}
             ly = {"norm1": f32(get(p + "norm1")), "dims": (H, G, d, dv),
                   "proj": lin(torch.cat([mw("q"), mw("k"), mw("g")], 0), bias), "out": lin(mw("o")),

@@ -1,7 +1,8 @@
-"""Throughput of the Golitar family at layer sizes of real models (random weights), beside the quantized Llama path at
-equal width / feed-forward / depth, with every operator of the step timed in place and set against its roofline.
+"""Throughput of the Golitar and Babodra families at layer sizes of real models (random weights), with every operator of
+the step timed in place and set against its roofline.  Golitar is shown beside the quantized Llama path at equal width /
+feed-forward / depth; Babodra beside Golitar at equal width / depth / active feed-forward size.
 
-``run(size, ...)`` is what ``bench.py --family golitar`` prints.  Method: one prompt of ``prompt`` tokens goes through
+``run(size, ...)`` is what ``bench.py --family golitar|babodra`` prints.  Method: one prompt of ``prompt`` tokens goes through
 ``HybridEngine.forward`` in portions of ``portion`` rows (prefill tok/s, CUDA events around all portions), then ``batch``
 sequences decode ``steps`` tokens each (decode tok/s).  The per-operator table wraps every library call of one prefill
 portion and one decode step in a CUDA event pair; bytes and flops are the algorithmic ones of the call's shapes, the
@@ -18,10 +19,14 @@ import torch
 SIZES = {
     # width, feed-forward, heads x dims of the delta mixer and of the attention mixer, layers as a pattern string
     "1b": dict(width=2048, ff=8192, vocab=32000, pattern="dddadddadddadddA", dH=16, dG=16, dk=128, dv=128, aH=16, aG=4,
-               ad=64, adv=128, window=1024, llama=dict(hidden_size=2048, intermediate_size=8192, num_attention_heads=32,
+               ad=64, adv=128, window=1024, bab=dict(heads=16, kv_heads=4, dim=128, pattern="dmmmdmmmdmmmdmmm", experts=16, top=4,
+                                                     groups=(4, 2), expert_ff=1536, shared_ff=2048),
+               llama=dict(hidden_size=2048, intermediate_size=8192, num_attention_heads=32,
                                                        num_key_value_heads=8, head_dim=64, vocab_size=32000)),
     "8b": dict(width=4096, ff=14336, vocab=32000, pattern="dddadddA", dH=32, dG=16, dk=128, dv=128, aH=32, aG=8, ad=64,
-               adv=128, window=2048, llama=dict(hidden_size=4096, intermediate_size=14336, num_attention_heads=32,
+               adv=128, window=2048, bab=dict(heads=32, kv_heads=8, dim=128, pattern="dmmmdmmm", experts=16, top=4, groups=(4, 2),
+                                              expert_ff=3072, shared_ff=2048),
+               llama=dict(hidden_size=4096, intermediate_size=14336, num_attention_heads=32,
                                                 num_key_value_heads=8, head_dim=128, vocab_size=32000)),
 }
 
@@ -42,6 +47,22 @@ def golitar_config(size: str) -> dict:
                                              "scaling": {"factor": 4.0, "low": 1.0, "high": 2.0, "original": 4096}}}})
     return {"architecture": "Golitar", "vocab": s["vocab"], "width": s["width"], "streams": 2, "norm": {"eps": 1e-5},
             "logit_softcap": 30.0, "layers": layers}
+
+
+def babodra_config(size: str, max_positions: int = 8192) -> dict:
+    """Same width and depth as golitar_config(size); a dense layer has the same feed-forward size and a mixture layer the
+    same ACTIVE size (top x expert ff + shared ff)."""
+    s = SIZES[size]
+    b = s["bab"]
+    mixer = {"heads": b["heads"], "kv_heads": b["kv_heads"], "dim": b["dim"], "vdim": b["dim"], "scale": b["dim"] ** -0.5,
+             "q_temp": {"coef": 0.1, "every": 1024}}
+    moe = {"kind": "moe", "expert": {"ff": b["expert_ff"]}, "shared": {"ff": b["shared_ff"]},
+           "router": {"experts": b["experts"], "top": b["top"], "scale": 2.5,
+                      "groups": {"count": b["groups"][0], "keep": b["groups"][1]}}}
+    dense = {"kind": "dense", "ff": s["ff"], "limit": 7.0}
+    layers = [{"type": "attention", "mixer": dict(mixer), "mlp": dict(dense if ch == "d" else moe)} for ch in b["pattern"]]
+    return {"architecture": "Babodra", "vocab": s["vocab"], "width": s["width"], "max_positions": max_positions,
+            "norm": {"eps": 1e-5}, "layers": layers}
 
 
 def _peaks(root):
@@ -86,6 +107,34 @@ def _cost(name, a, model, batch_info):
         wb = 4 if a[7] == 1 else 2
         extra = 2 * model.S * M * N * 4 if epi == 3 else M * N * ob
         return N * K * wb + M * K * act + extra, 2.0 * M * N * K, f"linear M={M}"
+    if name == "pieh_linear_glu":
+        M, N, K = a[8], a[9], a[10]
+        ob = 4 if a[1] == 1 else 2
+        wb = 4 if a[7] == 1 else 2
+        return N * K * wb + M * K * act + M * (N // 2) * ob, 2.0 * M * N * K, f"linear_glu M={M}"
+    if name == "pieh_moe_linear":
+        P, N, K, glu, E = a[9], a[10], a[11], a[13], a[17]._obj.E
+        ob = 4 if a[1] == 1 else 2
+        wb = 4 if a[7] == 1 else 2
+        return min(E, P) * N * K * wb + P * K * act + P * (N // 2 if glu else N) * ob, 2.0 * P * N * K, f"moe_linear P={P}"
+    if name == "pieh_moe_route":
+        pl = a[2]._obj
+        return a[3] * (pl.E * 4 + pl.top * 16 * 2), 0.0, "moe_route"
+    if name == "pieh_embed_positions":
+        return a[8] * a[9] * (2 * act + 4 + act), 0.0, "embed"
+    if name == "pieh_postnorm_add":
+        Tn, W, mix = a[7], a[8], a[4]
+        parts = (mix._obj.top + 1) if mix is not None else 1
+        return Tn * W * (4 * parts + 8 + act), 0.0, "postnorm_add" + ("(mixture)" if mix is not None else "")
+    if name.startswith("pieh_bias_attn"):
+        at = a[-3]._obj
+        H, G, d, dv = at.H, at.G, at.d, at.dv
+        if name == "pieh_bias_attn_prepare":
+            return T * ((H * d + G * d + G * dv + H * d) * 4 + G * (d + dv) * act), 0.0, "attn_prepare"
+        keys = ctx + T // max(n_seq, 1)
+        per_q = ctx + (T // max(n_seq, 1) + 1) / 2 if T > n_seq else keys
+        return (n_seq * keys * G * (d + dv) * act + T * H * (d * 4 + dv * (act + 4)), 2.0 * T * H * per_q * (d + dv),
+                "attn_run")
     if name in ("pieh_stream_norm",):
         R, S, W = a[8], a[9], a[10]
         return R * S * W * 4 + R * W * act, 0.0, "stream_norm"
@@ -126,16 +175,29 @@ def _table(timed, model, batch_info, hbm, tfl):
     return agg
 
 
-def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=".", with_llama=True) -> dict:
+def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=".", with_llama=True,
+        family="golitar") -> dict:
+    """family "golitar": beside the quantized Llama path (with_llama); "babodra": beside Golitar at equal size."""
     from .engine import HybridEngine
-    from .golitar import GolitarArgs, GolitarModel, random_weights
 
-    cfg = golitar_config(size)
-    args = GolitarArgs.from_dict(cfg)
     hbm, tfl, src = _peaks(root)
     t0 = time.time()
-    model = GolitarModel(args, random_weights(args, seed=0, device="cuda"), "cuda", "bfloat16")
-    n_params = sum(l.w.numel() for ly in model.layers for l in ly.values() if hasattr(l, "w")) + model.head.w.numel()
+    if family == "babodra":
+        from .babodra import BabodraArgs, BabodraModel, random_weights
+        cfg = babodra_config(size, max_positions=prompt + steps + warmup + 64)
+        args = BabodraArgs.from_dict(cfg)
+        weights = random_weights(args, seed=0, device="cuda")
+        n_params = sum(v.numel() for k, v in weights.items() if k != "pos")
+        model = BabodraModel(args, weights, "cuda", "bfloat16")
+        del weights
+        pattern = SIZES[size]["bab"]["pattern"]
+    else:
+        from .golitar import GolitarArgs, GolitarModel, random_weights
+        cfg = golitar_config(size)
+        args = GolitarArgs.from_dict(cfg)
+        model = GolitarModel(args, random_weights(args, seed=0, device="cuda"), "cuda", "bfloat16")
+        n_params = sum(l.w.numel() for ly in model.layers for l in ly.values() if hasattr(l, "w")) + model.head.w.numel()
+        pattern = SIZES[size]["pattern"]
     timed = _Timed(model.L)
     model.L = timed
     g = torch.Generator().manual_seed(1)
@@ -179,7 +241,7 @@ def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=
     torch.cuda.synchronize()
     pre_table = _table(timed, model, (portion, 1, 0), hbm, tfl)
     timed.on = False
-    out = {"family": "golitar", "size": size, "params": n_params, "layers": SIZES[size]["pattern"], "dtype": "bf16",
+    out = {"family": family, "size": size, "params": n_params, "layers": pattern, "dtype": "bf16",
            "data": "synthetic (random weights)", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src},
            "prefill": {"prompt": prompt, "portion": portion, "ms": round(prefill_ms, 2),
                        "tok_s": round(prompt / prefill_ms * 1e3, 1)},
@@ -190,7 +252,10 @@ def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=
            "pipeline_error": int(timed._lib.pieh_pipeline_error()), "setup_s": round(time.time() - t0, 1)}
     del eng, model
     torch.cuda.empty_cache()
-    if with_llama:
+    if family == "babodra":
+        if with_llama:      # the closest model of the framework at the same width, depth and active feed-forward size
+            out["golitar_equal_size"] = run(size, prompt, portion, batch, steps, warmup, root, with_llama=False)
+    elif with_llama:
         out["llama_equal_size"] = _llama(size, prompt, batch, steps, warmup)
     return out
 
