@@ -8,13 +8,20 @@
 //                       keys go to the key pages and the values -- here usually the PROJECTED keys themselves, v_off ==
 //                       k_off -- to the value pages at the token's position
 // bias_run_kernel       one CTA per (token, query head): 8 warps take 32-key blocks in turn with an online softmax each,
-//                       merged through shared memory together with the sink; serves decoding and every fp32 step
+//                       merged through shared memory together with the sink; serves decoding and every fp32 step.
+//                       When a step has few (token, head) pairs -- decoding -- a thread-block CLUSTER of 2 / 4 / 8 CTAs
+//                       shares one pair: each CTA takes a contiguous slice of the keys and the first CTA of the cluster
+//                       reads the others' partial softmax out of their shared memory (distributed shared memory), so a
+//                       long context is spread over the whole GPU without a workspace or a second launch
 // bias_tile_kernel      prompt portions over bf16 pages: 64-row query tiles on mma.sync (below)
 // A step's keys are appended before its queries run, so a prompt portion sees itself through the same pages as its past.
+#include <cooperative_groups.h>
+
 #include "hyb_common.cuh"
 
 namespace pieh {
 
+namespace cg = cooperative_groups;
 constexpr int kPage = 64;
 
 template <typename KT>
@@ -65,22 +72,27 @@ template <> struct ld8<__nv_bfloat16> {
   }
 };
 
-template <typename KT, typename OT, int NV>
+template <typename KT, typename OT, int NV, bool CLUSTER>
 __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const float* q, const float* proj, long long ld,
-                                                                  const pieh_bias_attn a, const pieh_batch b) {
+                                                                  const pieh_bias_attn a, const pieh_batch b, int cs) {
   extern __shared__ __align__(16) float sm[];
   constexpr int NW = kRunWarps, NTH = kRunWarps * 32;
   pdl_sync();
-  const int t = blockIdx.x / a.H, h = blockIdx.x - t * a.H;
+  const int pair = blockIdx.x / cs, rank = blockIdx.x - pair * cs;   // cs CTAs (one cluster) per (token, head)
+  const int t = pair / a.H, h = pair - t * a.H;
   const int g = h / (a.H / a.G);
   const int i = b.tok_seq[t], p = b.tok_pos[t];
   const int d = a.d, dv = a.dv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* qs = sm;              // [d]
-  float* mg = qs + d;          // [warps][dv + 2]: acc, m, l
+  float* qs = sm;                       // [d]
+  float* mg = qs + d;                   // [warps][dv + 2]: acc, m, l
+  float* part = mg + NW * (dv + 2);     // [dv + 2]: this CTA's merged partial softmax
   for (int c = threadIdx.x; c < d; c += NTH) qs[c] = q[((size_t)t * a.H + h) * d + c];
   __syncthreads();
   const int lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+  // this CTA's slice of the keys lo .. p: whole 32-key blocks, in order of rank
+  const int chunk = ((p - lo + cs) / cs + 31) / 32 * 32;
+  const int my_lo = lo + rank * chunk, my_hi = min(p, my_lo + chunk - 1);
   const float slope = a.slopes ? a.slopes[h] : 0.f;
   const int32_t* table = b.block_table + (size_t)i * b.bt_stride;
   const KT* kpool = reinterpret_cast<const KT*>(a.k_pages);
@@ -89,9 +101,9 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
   float m = -1e30f, l = 0.f, acc[NV];
 #pragma unroll
   for (int x = 0; x < NV; ++x) acc[x] = 0.f;
-  for (int base = lo + warp * 32; base <= p; base += NW * 32) {
+  for (int base = my_lo + warp * 32; base <= my_hi; base += NW * 32) {
     const int j = base + lane;
-    const bool ok = j <= p;
+    const bool ok = j <= my_hi;
     long long slot = 0;
     float s = -1e30f;
     if (ok) {
@@ -120,7 +132,7 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
     for (int x = 0; x < NV; ++x) acc[x] *= cf;
 #pragma unroll 1
     for (int k0 = 0; k0 < 32; k0 += 4) {
-      if (base + k0 > p) break;
+      if (base + k0 > my_hi) break;
       float w[4], vv[4][NV];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -148,20 +160,44 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
   if (lane == 0) { mine[dv] = m; mine[dv + 1] = l; }
   __syncthreads();
   const int c = threadIdx.x;   // dv <= 256 = threads
-  if (c < dv) {
-    float M = a.sink ? 0.f : -1e30f;   // the sink is one more partial softmax: maximum 0, sum 1, no values
+  if (c < dv) {                // the warps of this CTA -> one partial softmax
+    float M = -1e30f;
     for (int w = 0; w < NW; ++w) M = fmaxf(M, mg[(size_t)w * (dv + 2) + dv]);
-    float L = a.sink ? expf(-M) : 0.f, A = 0.f;
+    float L = 0.f, A = 0.f;
     for (int w = 0; w < NW; ++w) {
       const float* src = mg + (size_t)w * (dv + 2);
       const float f = expf(src[dv] - M);
       L = fmaf(src[dv + 1], f, L);
       A = fmaf(src[c], f, A);
     }
+    part[c] = A;
+    if (c == 0) { part[dv] = M; part[dv + 1] = L; }
+  }
+  if (CLUSTER) cg::this_cluster().sync(); else __syncthreads();
+  if (rank == 0 && c < dv) {   // the CTAs of the cluster and the sink -> the output
+    float M = a.sink ? 0.f : -1e30f;   // the sink is one more partial softmax: maximum 0, sum 1, no values
+    float L = 0.f, A = 0.f;
+    if (CLUSTER) {
+      cg::cluster_group cl = cg::this_cluster();
+      for (int r = 0; r < cs; ++r) M = fmaxf(M, cl.map_shared_rank(part, r)[dv]);
+      for (int r = 0; r < cs; ++r) {
+        const float* src = cl.map_shared_rank(part, r);
+        const float f = expf(src[dv] - M);
+        L = fmaf(src[dv + 1], f, L);
+        A = fmaf(src[c], f, A);
+      }
+    } else {
+      M = fmaxf(M, part[dv]);
+      const float f = expf(part[dv] - M);
+      L = part[dv + 1] * f;
+      A = part[c] * f;
+    }
+    if (a.sink) L += expf(-M);
     float o = A / L;
     if (a.g_off >= 0) o *= 1.f / (1.f + expf(-proj[(size_t)t * ld + a.g_off + (size_t)h * dv + c]));
     elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, o);
   }
+  if (CLUSTER) cg::this_cluster().sync();   // nobody's shared memory goes away while the first CTA still reads it
 }
 
 // ---- prompt portions on the tensor cores ---------------------------------------------------------------------------
@@ -380,16 +416,40 @@ static bool bias_attn_ok(const pieh_bias_attn* a) {
          a->k_pages && a->v_pages && a->temp_every >= 0 && a->window >= 0 && a->k_off >= 0 && a->v_off >= 0;
 }
 
+template <typename KT, typename OT, int NV>
+static cudaError_t launch_run_nv(OT* out, const float* q, const float* proj, long long ld, const pieh_bias_attn& a,
+                                 const pieh_batch& b, cudaStream_t st) {
+  const size_t smem = ((size_t)a.d + (kRunWarps + 1) * (a.dv + 2)) * 4;
+  const long long pairs = (long long)b.T * a.H;
+  // few (token, head) pairs: clusters of CTAs share a pair's keys until the GPU is covered a few times over
+  const long long want = 4LL * num_sms();
+  const int cs = pairs * 8 <= want ? 8 : pairs * 4 <= want ? 4 : pairs * 2 <= want ? 2 : 1;
+  if (cs == 1) return launch_k(bias_run_kernel<KT, OT, NV, false>, dim3((unsigned)pairs), dim3(kRunWarps * 32), smem, st, out, q, proj, ld, a, b, 1);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(pairs * cs));
+  cfg.blockDim = dim3(kRunWarps * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, bias_run_kernel<KT, OT, NV, true>, out, q, proj, ld, a, b, cs);
+}
+
 template <typename KT, typename OT>
 static cudaError_t launch_run(OT* out, const float* q, const float* proj, long long ld, const pieh_bias_attn& a,
                               const pieh_batch& b, cudaStream_t st) {
-  const size_t smem = ((size_t)a.d + kRunWarps * (a.dv + 2)) * 4;
-  const unsigned grid = (unsigned)b.T * a.H;
-  const int nv = (a.dv + 31) / 32, nth = kRunWarps * 32;
-  if (nv <= 1) return launch_k(bias_run_kernel<KT, OT, 1>, dim3(grid), dim3(nth), smem, st, out, q, proj, ld, a, b);
-  if (nv <= 2) return launch_k(bias_run_kernel<KT, OT, 2>, dim3(grid), dim3(nth), smem, st, out, q, proj, ld, a, b);
-  if (nv <= 4) return launch_k(bias_run_kernel<KT, OT, 4>, dim3(grid), dim3(nth), smem, st, out, q, proj, ld, a, b);
-  return launch_k(bias_run_kernel<KT, OT, 8>, dim3(grid), dim3(nth), smem, st, out, q, proj, ld, a, b);
+  const int nv = (a.dv + 31) / 32;
+  if (nv <= 1) return launch_run_nv<KT, OT, 1>(out, q, proj, ld, a, b, st);
+  if (nv <= 2) return launch_run_nv<KT, OT, 2>(out, q, proj, ld, a, b, st);
+  if (nv <= 4) return launch_run_nv<KT, OT, 4>(out, q, proj, ld, a, b, st);
+  return launch_run_nv<KT, OT, 8>(out, q, proj, ld, a, b, st);
 }
 
 }  // namespace pieh

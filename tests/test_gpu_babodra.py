@@ -341,3 +341,59 @@ def test_greedy_generation_through_the_engine():
             if float(top2[0] - top2[1]) > 1e-3:
                 assert int(lg.argmax()) == tok
             seq.append(tok)
+
+
+def test_decode_attention_spread_over_a_cluster():
+    """Few (token, head) pairs make clusters of CTAs share a pair's keys; contexts that do not fill every CTA's slice,
+    end inside a 32-key block or leave whole CTAs without keys must give what one CTA alone gives (a prompt run)."""
+    cfg, w, model = make(kinds=[None], n_layers=1, heads=2, kv_heads=1, dim=24, width=40, max_positions=700)
+    ids = toks(640)
+    want = O.forward(cfg, w, ids)
+    eng = engine(model, graph=False)
+    for start in (1, 30, 33, 255, 257, 600):
+        eng.forward([("s", ids[:start], [])])
+        got = [eng.forward([("s", [ids[t]], [0])]) for t in range(start, start + 36)]
+        eng.finish("s")
+        assert err(torch.cat(got), want[start: start + 36]) < TOL32, start
+
+
+def test_checkpoint_on_disk_through_the_command_line(tmp_path):
+    """config.json + model.safetensors -> registry -> bin/trace_run (a sequence ended and its slot re-used) and the
+    `generate` command."""
+    import json, os, subprocess, sys
+    import numpy as np
+    from safetensors.torch import save_file
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, w, model = make(dtype="float32")
+    del model
+    mdir, out = tmp_path / "m", tmp_path / "o"
+    mdir.mkdir()
+    save_file({k: v.contiguous() for k, v in w.items()}, str(mdir / "model.safetensors"))
+    (mdir / "config.json").write_text(json.dumps(cfg))
+    a, b = toks(70, seed=90), toks(9, seed=91)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:66], "want": [0, 65]}, {"id": "b", "tokens": b, "want": [8]}],
+              "end": ["b"]},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[66:], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "c", "tokens": b[:4], "want": [3]}, {"id": "a", "tokens": [a[0]], "want": [0]}],
+              "end": ["a", "c"]}]
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(mdir), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "192", "--max-seqs", "2"], input="\n".join(json.dumps(x) for x in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert not (out / "1.f32").exists()
+    ra, rb = O.forward(cfg, w, a + [a[0]]), O.forward(cfg, w, b)
+    got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(3, -1).copy())
+    got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(2, -1).copy())
+    assert err(got0, torch.stack([ra[0], ra[65], rb[8]])) < TOL32
+    assert err(got2, torch.stack([rb[3], ra[70]])) < TOL32
+    g = subprocess.run([sys.executable, "-m", "proxy_inference_engine_b200", "generate", "--model", str(mdir), "--prompt-ids",
+                        ",".join(map(str, b)), "--max-new-tokens", "5", "--dtype", "float32"], cwd=root, capture_output=True,
+                       text=True, timeout=600)
+    assert g.returncode == 0, g.stderr[-2000:]
+    rec = json.loads(g.stdout.strip().splitlines()[-1])
+    assert rec["prompt_ids"] == b and len(rec["generated_ids"]) == 5
+    ref = O.forward(cfg, w, b + rec["generated_ids"])
+    for jj, tok in enumerate(rec["generated_ids"]):
+        row = ref[len(b) - 1 + jj]
+        assert float(row.max() - row[tok]) < 1e-3
