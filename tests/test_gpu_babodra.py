@@ -303,9 +303,10 @@ def test_long_decoding_through_captured_steps():
 @pytest.mark.parametrize("kw", [dict(heads=1, kv_heads=1, dim=8, width=24), dict(heads=6, kv_heads=1, dim=24),
                                 dict(heads=3, kv_heads=3, dim=40, width=56, ff=33, expert_ff=17, shared_ff=9),
                                 dict(experts=4, top=4, groups=(1, 1), shared_ff=0), dict(experts=7, top=1, groups=(7, 1)),
-                                dict(q_temp=None), dict(q_temp=(1.3, 1)), dict(heads=2, kv_heads=1, dim=64, width=128)],
+                                dict(q_temp=None), dict(q_temp=(1.3, 1)), dict(heads=2, kv_heads=1, dim=64, width=128),
+                                dict(heads=2, kv_heads=2, dim=128, width=64, kinds=[None, "dense"], n_layers=2)],
                          ids=["one-head", "one-kv-head", "odd-sizes", "all-experts", "top-1", "no-temperature",
-                              "temperature-every-1", "tile-head-size"])
+                              "temperature-every-1", "tile-head-size", "tile-head-size-128"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_other_sizes(kw, dtype):
     cfg, w, model = make(dtype=dtype, **kw)
