@@ -194,13 +194,59 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Many rows, few outputs (N <= NMAX <= 32; a router): a warp per activation row, its lanes cutting K in 8-element
+// pieces; the whole weight matrix is a few tens of KB and stays in L1 / L2, so the kernel reads x once -- the tensor-core
+// tiles would spend a 256-column tile on a handful of columns.
+template <typename XT, typename WT, typename OT, int NMAX>
+__global__ void __launch_bounds__(256) linear_skinny_kernel(const LinArgs a) {
+  pdl_sync();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * 8 + warp;
+  if (m >= a.M) return;
+  const XT* x = reinterpret_cast<const XT*>(a.x) + (size_t)m * a.x_ld;
+  const WT* w = reinterpret_cast<const WT*>(a.w);
+  float acc[NMAX];
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) acc[n] = 0.f;
+  for (int k = lane * 8; k < a.K; k += 256) {
+    float xv[8];
+    vec8<XT>::load(x + k, xv);
+    if (sizeof(XT) != sizeof(WT)) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) xv[i] = elem<WT>::round(xv[i]);
+    }
+#pragma unroll
+    for (int n = 0; n < NMAX; ++n) {
+      if (n < a.N) {
+        float wv[8];
+        vec8<WT>::load(w + (size_t)n * a.K + k, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[n] = fmaf(xv[i], wv[i], acc[n]);
+      }
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < NMAX; ++n) {
+    if (n < a.N) {
+      const float y = warp_sum(acc[n]);
+      if (lane == 0) lin_store<OT>(a, m, n, y);
+    }
+  }
+}
+
 template <typename XT, typename WT, typename OT>
 static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
   const bool vec_ok = a.K % 8 == 0 && a.x_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 31) == 0 &&
                       (reinterpret_cast<uintptr_t>(a.w) & 31) == 0;
   count_launch();
   cudaError_t e = cudaSuccess;
-  if (a.g_tiles) {
+  if (!a.g_tiles && a.M > 32 && a.N <= 32 && vec_ok && a.epi != PIEH_EPI_GLU) {
+    const dim3 grid((a.M + 7) / 8);
+    if (a.N <= 8) e = launch_k(linear_skinny_kernel<XT, WT, OT, 8>, grid, dim3(256), 0, st, a);
+    else if (a.N <= 16) e = launch_k(linear_skinny_kernel<XT, WT, OT, 16>, grid, dim3(256), 0, st, a);
+    else e = launch_k(linear_skinny_kernel<XT, WT, OT, 32>, grid, dim3(256), 0, st, a);
+  } else if (a.g_tiles) {
     // grouped: few slots -> a CTA per (slot, output rows) streaming that slot's expert; else 64-slot tiles of one expert
     if (a.M <= 32 && vec_ok) {
       const bool wide = (long long)a.N * a.M >= 4 * 4 * num_sms();

@@ -248,6 +248,9 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
 bool linear_umma_ok(const LinArgs& a, int x_dtype, int w_dtype) {
   static const bool off = [] { const char* e = getenv("PIE_HYBRID_NO_UMMA"); return e && e[0] == '1'; }();
   if (off) return false;
+  if (!a.g_tiles && a.N <= 32 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 31) == 0 &&
+      (reinterpret_cast<uintptr_t>(a.x) & 31) == 0 && a.epi != PIEH_EPI_GLU)
+    return false;   // a handful of output columns: linear_skinny_kernel reads x once instead of filling 256-column tiles
   return x_dtype == PIE_DTYPE_BF16 && w_dtype == PIE_DTYPE_BF16 && a.M > 32 && a.K % kBK == 0 && a.x_ld % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
 }

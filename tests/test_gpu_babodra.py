@@ -118,6 +118,22 @@ def test_gated_pair_epilogue_in_every_linear_kernel():
                 assert err(out, want) < 1e-5, (M, ff, K, exact, alpha)
 
 
+def test_router_sized_products():
+    """pieh_linear with many rows and a handful of outputs (the kernel with a warp per row), both precisions, with bias."""
+    L = lib()
+    g = torch.Generator().manual_seed(5)
+    for M, N, K in [(100, 17, 256), (70, 7, 64), (40, 32, 200), (33, 1, 72), (4096, 9, 128)]:
+        for exact in (True, False):
+            x = torch.randn((M, K), generator=g)
+            wt = (torch.randn((N, K), generator=g) / K ** 0.5).to(torch.bfloat16)
+            bias = torch.randn((N,), generator=g).cuda()
+            code, dt = (1, torch.float32) if exact else (0, torch.bfloat16)
+            xd, wd = x.to(dt).cuda(), wt.to(dt).cuda()
+            out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+            assert L.pieh_linear(p_(out), 1, N, p_(xd), code, K, p_(wd), code, p_(bias), M, N, K, 0, 0.0, None, None, 0, None) == 0
+            assert err(out, xd.double().cpu() @ wt.double().T + bias.double().cpu()) < 1e-5, (M, N, K, exact)
+
+
 @pytest.mark.parametrize("E,top,groups,keep", [(6, 2, 3, 2), (8, 4, 2, 1), (5, 1, 1, 1), (4, 4, 4, 4), (12, 3, 6, 2), (64, 6, 8, 3)])
 def test_routing_alone(E, top, groups, keep):
     """pieh_moe_route against the restatement: choices, weights, and a plan whose slots are a permutation sorted by expert."""
