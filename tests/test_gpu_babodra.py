@@ -216,9 +216,65 @@ def test_distance_bias_and_sink_show_in_one_head():
     """One query is made to match one far key strongly: the output then depends on the exact distance term and on the
     sink's share, which random weights would drown among hundreds of keys."""
     cfg, w, model = make(kinds=[None], n_layers=1, heads=4, kv_heads=4, dim=16, width=64, scale=2.0,
-                         edit={"l0.mix.q": lambda t: t * 4, "l0.mix.k": lambda t: t * 4})
+                         edit={"l0.mix.q.norm": lambda t: t * 2, "l0.mix.k.norm": lambda t: t * 2})
     ids = toks(300)
     assert err(whole(engine(model), ids), O.forward(cfg, w, ids)) < TOL32
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_planted_far_keys_in_the_attention_operator(dtype):
+    """pieh_bias_attn_prepare / _run on given projections, no norms: chosen queries are made to match ONE far key (the
+    first position, the last and first slot of a page, the key just before the query), so every output row is that key's
+    value times a weight set by the exact distance term and the sink.  Scattered pages; the prompt in portions and single
+    rows, which takes the tile kernel (bf16), the row kernel and its cluster form through the same positions."""
+    from proxy_inference_engine_b200._lib import HybBiasAttn
+    from proxy_inference_engine_b200.ragged import BatchDetails
+    L = lib()
+    H, G, d, T, scale = 4, 2, 64, 450, 0.125
+    g = torch.Generator().manual_seed(11)
+    q, k = 0.3 * torch.randn((T, H, d), generator=g), torch.randn((T, G, d), generator=g)
+    v, gate = torch.randn((T, G, d), generator=g), torch.randn((T, H * d), generator=g)
+    plant = {449: 0, 448: 63, 447: 64, 446: 127, 445: 128, 444: 443, 300: 1, 200: 199, 129: 128, 128: 127, 65: 64, 64: 0}
+    for i, j in plant.items():
+        for h in range(H):
+            kj = k[j, h // (H // G)]
+            q[i, h] = (6.0 + 2.0 * h) / scale * kj / kj.norm() ** 2      # score 6 + 2 h before the distance term
+    exact = dtype == "float32"
+    rnd = O.ident if exact else O.bf16_round
+    slopes = O.head_slopes(H)
+    want = O.sink_attention(rnd(q.double()), rnd(k.double()), rnd(v.double()), scale, slopes, H // G)
+    want = want.reshape(T, H * d) * torch.sigmoid(gate.double())
+    # the restatement itself must rest on the planted key: row 449 of the flattest head is mostly the value at position 0
+    flat = want.view(T, H, d)[449, H - 1] / torch.sigmoid(gate.double()).view(T, H, d)[449, H - 1]
+    v0 = rnd(v.double())[0, G - 1]
+    assert float((flat @ v0) / (v0 @ v0)) > 0.5
+    proj = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), gate], 1).cuda().contiguous()
+    ld = proj.shape[1]
+    code, dt = (1, torch.float32) if exact else (0, torch.bfloat16)
+    pages = [5, 2, 7, 0, 3, 1, 6, 4]
+    kp = torch.zeros((8, 64, G, d), dtype=dt, device="cuda")
+    vp = torch.zeros_like(kp)
+    sl = slopes.float().cuda()
+    at = HybBiasAttn(H, G, d, d, H * d, H * d + G * d, H * d + 2 * G * d, None, None, 1e-5, scale, 0.0, 0, p_(sl), 1, 0,
+                     p_(kp), p_(vp), code)
+    got, ctx = [], 0
+    for n in [200, 3] + [1] * 12 + [229] + [1] * 6:
+        batch = BatchDetails.build([("s", [0] * n, ctx, pages)], device="cuda")
+        desc, keep = batch.hybrid_descriptor()
+        rows = proj[ctx: ctx + n]
+        qo = torch.empty((n, H * d), dtype=torch.float32, device="cuda")
+        out = torch.empty((n, H * d), dtype=dt, device="cuda")
+        assert L.pieh_bias_attn_prepare(p_(qo), p_(rows), ld, C.byref(at), C.byref(desc), None) == 0
+        assert L.pieh_bias_attn_run(p_(out), code, p_(qo), p_(rows), ld, C.byref(at), C.byref(desc), None) == 0
+        torch.cuda.synchronize()
+        got.append(out.float())
+        ctx += n
+    got = torch.cat(got).double().cpu()
+    assert ctx == T
+    tol = 1e-5 if exact else 2e-2
+    for i in plant:
+        assert float((got[i] - want[i]).abs().max()) < tol * float(want[i].abs().max()), i
+    assert float((got - want).abs().max()) < tol * float(want.abs().max())
 
 
 # ---- schedules --------------------------------------------------------------------------------------------------------
