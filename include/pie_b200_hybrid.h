@@ -171,7 +171,7 @@ typedef struct pieh_bias_attn {
   float eps;
   float scale;
   float temp_coef;
-  int temp_every;
+  double temp_every;     /* positions per temperature step (need not be whole); 0 = no temperature */
   const float* slopes;     /* [H] or NULL = no distance bias */
   int sink;
   int window;

@@ -163,7 +163,7 @@ class HybBiasAttn(C.Structure):
     """pieh_bias_attn"""
     _fields_ = [("H", C.c_int), ("G", C.c_int), ("d", C.c_int), ("dv", C.c_int), ("k_off", C.c_longlong),
                 ("v_off", C.c_longlong), ("g_off", C.c_longlong), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
-                ("eps", C.c_float), ("scale", C.c_float), ("temp_coef", C.c_float), ("temp_every", C.c_int),
+                ("eps", C.c_float), ("scale", C.c_float), ("temp_coef", C.c_float), ("temp_every", C.c_double),
                 ("slopes", C.c_void_p), ("sink", C.c_int), ("window", C.c_int), ("k_pages", C.c_void_p),
                 ("v_pages", C.c_void_p), ("kv_dtype", C.c_int)]
 

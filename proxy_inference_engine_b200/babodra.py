@@ -125,7 +125,7 @@ class BabodraModel:
             ly = {"norm1": f32(get(p + "norm1")), "dims": (H, G, d, dv),
                   "proj": lin(torch.cat([mw("q"), mw("k"), mw("g")], 0), bias), "out": lin(mw("o")),
                   "q_norm": f32(mw("q.norm")), "k_norm": f32(mw("k.norm")), "scale": float(m["scale"]),
-                  "temp": (float(qt.get("coef") or 0.0), int(qt.get("every") or 0)),
+                  "temp": (float(qt.get("coef") or 0.0), float(qt.get("every") or 0.0)),
                   "slopes": torch.tensor([2.0 ** (-SLOPE_EXPONENT * (h + 1) / H) for h in range(H)], dtype=torch.float32,
                                          device=device),
                   "mlp": None}

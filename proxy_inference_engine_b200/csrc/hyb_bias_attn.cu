@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(256) bias_prepare_kernel(float* q_out, const f
     for (int c = threadIdx.x; c < nk; c += blockDim.x) ss = fmaf(row[a.k_off + c], row[a.k_off + c], ss);
     ik = 1.f / sqrtf(block_sum(ss, red) / (float)nk + a.eps);
   }
-  if (a.temp_every > 0) iq *= 1.f + a.temp_coef * logf((float)((p + 1) / a.temp_every) + 1.f);
+  if (a.temp_every > 0.0) iq *= 1.f + a.temp_coef * logf((float)floor((double)(p + 1) / a.temp_every) + 1.f);
   const size_t slot = (size_t)b.block_table[(size_t)i * b.bt_stride + p / kPage] * kPage + p % kPage;
   KT* kp = reinterpret_cast<KT*>(a.k_pages) + slot * nk;
   KT* vp = reinterpret_cast<KT*>(a.v_pages) + slot * nv;
@@ -413,7 +413,7 @@ static bool tile_ok(const pieh_bias_attn& a, const pieh_batch& b, int out_dtype)
 
 static bool bias_attn_ok(const pieh_bias_attn* a) {
   return a && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->d > 0 && a->dv > 0 && a->dv <= 256 && a->d <= 1024 &&
-         a->k_pages && a->v_pages && a->temp_every >= 0 && a->window >= 0 && a->k_off >= 0 && a->v_off >= 0;
+         a->k_pages && a->v_pages && a->temp_every >= 0.0 && a->window >= 0 && a->k_off >= 0 && a->v_off >= 0;
 }
 
 template <typename KT, typename OT, int NV>

@@ -255,7 +255,7 @@ def test_planted_far_keys_in_the_attention_operator(dtype):
     kp = torch.zeros((8, 64, G, d), dtype=dt, device="cuda")
     vp = torch.zeros_like(kp)
     sl = slopes.float().cuda()
-    at = HybBiasAttn(H, G, d, d, H * d, H * d + G * d, H * d + 2 * G * d, None, None, 1e-5, scale, 0.0, 0, p_(sl), 1, 0,
+    at = HybBiasAttn(H, G, d, d, H * d, H * d + G * d, H * d + 2 * G * d, None, None, 1e-5, scale, 0.0, 0.0, p_(sl), 1, 0,
                      p_(kp), p_(vp), code)
     got, ctx = [], 0
     for n in [200, 3] + [1] * 12 + [229] + [1] * 6:
@@ -375,10 +375,10 @@ def test_long_decoding_through_captured_steps():
 @pytest.mark.parametrize("kw", [dict(heads=1, kv_heads=1, dim=8, width=24), dict(heads=6, kv_heads=1, dim=24),
                                 dict(heads=3, kv_heads=3, dim=40, width=56, ff=33, expert_ff=17, shared_ff=9),
                                 dict(experts=4, top=4, groups=(1, 1), shared_ff=0), dict(experts=7, top=1, groups=(7, 1)),
-                                dict(q_temp=None), dict(q_temp=(1.3, 1)), dict(heads=2, kv_heads=1, dim=64, width=128),
+                                dict(q_temp=None), dict(q_temp=(1.3, 1)), dict(q_temp=(0.4, 2.5)), dict(heads=2, kv_heads=1, dim=64, width=128),
                                 dict(heads=2, kv_heads=2, dim=128, width=64, kinds=[None, "dense"], n_layers=2)],
                          ids=["one-head", "one-kv-head", "odd-sizes", "all-experts", "top-1", "no-temperature",
-                              "temperature-every-1", "tile-head-size", "tile-head-size-128"])
+                              "temperature-every-1", "temperature-every-2.5", "tile-head-size", "tile-head-size-128"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_other_sizes(kw, dtype):
     cfg, w, model = make(dtype=dtype, **kw)
